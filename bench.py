@@ -1,0 +1,401 @@
+#!/usr/bin/env python
+"""Benchmark of the talker attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload at N = 1 ("ragged_decode_b64"): batched ragged decode attention in the Qwen3-TTS 1.7B talker shape -
+64 streams, KV lengths uniform in [256, 4096] (SplitMix64 seed 1), 16 query / 8 KV heads, head_dim 128, paged bf16
+KV cache with 64-token pages and a shuffled page table, QK-RMSNorm + RoPE (theta 1e6) fused into the append.
+One step = one decode token through all 28 layers' attention path: per layer the fused norm + RoPE + paged append
+and the split-KV attention over every stream.  Each layer has its own pools (about 0.57 GB of KV per layer), so
+consecutive launches never find their input in the 126 MB L2.
+
+With N > 1 every rank runs the same workload on its own streams and pool (streams are independent: no collective
+on the data path); the reported value is all ranks' bytes over the slowest rank's time (weak scaling).
+
+`--impl reference` times the CPU restatement of the reference's attention (the reference has no CPU
+implementation of its own; see the oracle's header) on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+Q_HEADS, KV_HEADS, D, PAGE = 16, 8, 128, 64
+LAYERS = 28
+BATCH = 64
+LEN_LO, LEN_HI = 256, 4096
+METRIC = "decode attn HBM GB/s"
+WORKLOAD = "ragged_decode_b64"
+
+
+def splitmix64_ints(seed, lo, hi, n):
+    """lo + next_u64() % (hi - lo + 1), SplitMix64 - same recipe as the tests, in pure Python for the bench."""
+    mask = (1 << 64) - 1
+    state, out = seed & mask, []
+    for _ in range(n):
+        state = (state + 0x9E3779B97F4A7C15) & mask
+        z = state
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+        z ^= z >> 31
+        out.append(lo + z % (hi - lo + 1))
+    return np.array(out, dtype=np.int32)
+
+
+def workload_lengths(rank=0):
+    """Existing KV length per stream; the timed step appends one token and attends length + 1 keys."""
+    return splitmix64_ints(1 * 1000 + 99 + 7919 * rank, LEN_LO, LEN_HI, BATCH)
+
+
+def algorithmic_bytes_per_layer(lengths):
+    # K and V rows of every attended key (2 * 8 heads * 128 * 2 B = 4096 B per key) + q, out, appended rows
+    return int((lengths.astype(np.int64) + 1).sum()) * 4096 + len(lengths) * 12288
+
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            cols = [c.strip() for c in line.split(",")]
+            if len(cols) < 9:
+                continue
+            try:
+                sm.append(float(cols[1]))
+                smax.append(float(cols[2]))
+            except ValueError:
+                continue
+            for name, col in zip(names, cols[5:9]):
+                if col.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smax)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def load_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return float(data["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------- reference arm (CPU)
+
+def cpu_attention_sample(q_rot_bits, key_caches, value_caches, key_lens, repeats):
+    """Times the oracle's reference-faithful decode attention (all host threads) on the given streams."""
+    from oracle import qm_oracle as oracle
+
+    best = float("inf")
+    out = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        out = oracle.decode_attention(q_rot_bits, key_caches, value_caches, key_lens, mode="ref")
+        best = min(best, time.perf_counter() - t0)
+    return best, out
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import qm_oracle as oracle
+
+    lengths = workload_lengths()
+    sample = list(range(0, BATCH, 4))            # 16 of the 64 streams, every fourth
+    lens = lengths[sample]
+    key_caches = [oracle.normal_bf16(50 + i, (KV_HEADS, int(n) + 1, D)) for i, n in enumerate(lens)]
+    value_caches = [oracle.normal_bf16(150 + i, (KV_HEADS, int(n) + 1, D)) for i, n in enumerate(lens)]
+    q_rot = oracle.normal_bf16(250, (len(sample), Q_HEADS, D))
+    bytes_per_step = algorithmic_bytes_per_layer(lens)
+    for _ in range(args.warmup):
+        oracle.decode_attention(q_rot, key_caches, value_caches, lens + 1, mode="ref")
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.decode_attention(q_rot, key_caches, value_caches, lens + 1, mode="ref")
+    seconds = time.perf_counter() - t0
+    gbs = bytes_per_step * args.steps / seconds / 1e9
+    cores = host_cores()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "streams": BATCH, "kv_len": [LEN_LO, LEN_HI], "q_heads": Q_HEADS,
+                   "kv_heads": KV_HEADS, "head_dim": D, "page_tokens": PAGE,
+                   "note": "one step = one layer of decode attention over the sample, CPU"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{len(sample)} of {BATCH} streams (every 4th), one layer per step, "
+                                   "bf16-faithful restatement of the reference kernels, OpenMP over (stream, kv head)"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------- our arm (GPU)
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    pkg = entry.load_package()
+    pkg.load_library()
+
+    lengths = workload_lengths(rank)
+    pages_per_stream = (lengths + 1 + PAGE - 1) // PAGE
+    max_pages = int(pages_per_stream.max())
+    num_pages = int(pages_per_stream.sum())
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1000 + rank)
+    eng = pkg.TalkerAttention(layers=LAYERS, num_pages=num_pages, q_heads=Q_HEADS, kv_heads=KV_HEADS,
+                              max_positions=LEN_HI + 2)
+    for layer in range(LAYERS):
+        for view in eng.pool_view(layer):
+            view.normal_(generator=gen)
+    perm = torch.randperm(num_pages, generator=gen, device="cuda").to(torch.int32).cpu().numpy()
+    table = np.zeros((BATCH, max_pages), dtype=np.int32)
+    cursor = 0
+    for s in range(BATCH):
+        n = int(pages_per_stream[s])
+        table[s, :n] = perm[cursor:cursor + n]
+        cursor += n
+    page_table = torch.from_numpy(table).cuda()
+    positions = torch.from_numpy(lengths).cuda()
+    seq_lens = torch.from_numpy(lengths + 1).cuda()
+    ones = torch.ones(D, dtype=torch.bfloat16, device="cuda")
+
+    def randn_bf16(*shape):
+        return torch.randn(*shape, generator=gen, device="cuda").to(torch.bfloat16)
+
+    q = randn_bf16(LAYERS, BATCH, Q_HEADS, D)
+    k = randn_bf16(LAYERS, BATCH, KV_HEADS, D)
+    v = randn_bf16(LAYERS, BATCH, KV_HEADS, D)
+    q_rot = torch.empty_like(q)
+    out = torch.empty_like(q)
+    eng.workspace(BATCH)
+
+    def step_device():
+        for layer in range(LAYERS):
+            eng.launch_qk_norm_rope_cache_m1(layer, q[layer], k[layer], v[layer], ones, ones, positions, page_table,
+                                             q_rot=q_rot[layer])
+            eng.launch_attention(layer, q_rot[layer], seq_lens, page_table, out=out[layer])
+
+    # host-buffer path: per layer the step's q/k/v come from pinned host memory and the context goes back
+    def pinned(src):
+        host = torch.empty(src.shape, dtype=src.dtype).pin_memory()
+        host.copy_(src.cpu())
+        return host
+
+    q_host, k_host, v_host = pinned(q), pinned(k), pinned(v)
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    q_dev = torch.empty((BATCH, Q_HEADS, D), dtype=torch.bfloat16, device="cuda")
+    k_dev = torch.empty((BATCH, KV_HEADS, D), dtype=torch.bfloat16, device="cuda")
+    v_dev = torch.empty((BATCH, KV_HEADS, D), dtype=torch.bfloat16, device="cuda")
+    h2d_bytes = LAYERS * (q_dev.numel() + k_dev.numel() + v_dev.numel()) * 2
+    d2h_bytes = LAYERS * BATCH * Q_HEADS * D * 2
+
+    def step_e2e():
+        for layer in range(LAYERS):
+            q_dev.copy_(q_host[layer], non_blocking=True)
+            k_dev.copy_(k_host[layer], non_blocking=True)
+            v_dev.copy_(v_host[layer], non_blocking=True)
+            eng.launch_qk_norm_rope_cache_m1(layer, q_dev, k_dev, v_dev, ones, ones, positions, page_table,
+                                             q_rot=q_rot[layer])
+            eng.launch_attention(layer, q_rot[layer], seq_lens, page_table, out=out[layer])
+            out_host[layer].copy_(out[layer], non_blocking=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        barrier()
+        ms = start.elapsed_time(end)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.3)
+    total_ms = timed(step_device, args.steps)
+    # the attention bucket alone (split-KV kernel + combine), per launch, on the launching stream
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(LAYERS)]
+    attn_samples = []
+    for _ in range(max(2, min(args.steps, 5))):
+        torch.cuda.synchronize()
+        for layer in range(LAYERS):
+            eng.launch_qk_norm_rope_cache_m1(layer, q[layer], k[layer], v[layer], ones, ones, positions, page_table,
+                                             q_rot=q_rot[layer])
+            ev[layer][0].record()
+            eng.launch_attention(layer, q_rot[layer], seq_lens, page_table, out=out[layer])
+            ev[layer][1].record()
+        torch.cuda.synchronize()
+        attn_samples += [a.elapsed_time(b) for a, b in ev]
+    for _ in range(2):
+        step_e2e()
+    e2e_ms = timed(step_e2e, args.steps)
+    clocks = sampler.stop()
+    status = eng.status()
+
+    layer_bytes = algorithmic_bytes_per_layer(lengths)
+    if world > 1:
+        t = torch.tensor([float(layer_bytes)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t)
+        total_layer_bytes = float(t.item())
+    else:
+        total_layer_bytes = float(layer_bytes)
+    ms_per_step = total_ms / args.steps
+    value = total_layer_bytes * LAYERS / (ms_per_step * 1e-3) / 1e9
+    e2e_value = total_layer_bytes * LAYERS / (e2e_ms / args.steps * 1e-3) / 1e9
+    attn_ms = float(np.mean(attn_samples))
+    attn_bytes = layer_bytes - BATCH * 4096          # attention reads K/V/q and writes out; the append rows are the other kernel's
+    peak, peak_kind = load_peaks()
+    achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "streams_per_gpu": BATCH, "kv_len": [LEN_LO, LEN_HI], "q_heads": Q_HEADS,
+                   "kv_heads": KV_HEADS, "head_dim": D, "page_tokens": PAGE, "layers_per_step": LAYERS,
+                   "parallelism": f"streams x{world}",
+                   "l2": "each layer reads its own 0.57 GB of KV; inputs larger than the 126 MB L2"},
+        "us_per_layer": ms_per_step * 1e3 / LAYERS,
+        "attention_us_per_layer": attn_ms * 1e3,
+        "pct_of_measured_hbm_peak": 100.0 * value / world / peak,
+        "pct_of_nominal_8tbs": 100.0 * value / world / 8000.0,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                "ms_per_step": e2e_ms / args.steps,
+                "note": "q/k/v of each layer copied from pinned host memory, context copied back, inside the timed "
+                        "region; the KV cache is device-resident state by design"},
+        "gpu_launches": args.steps * LAYERS * 3,
+        "roofline": {"bound": "hbm", "kernel": "qm_decode_splitkv_kernel (+ combine)", "achieved": achieved,
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "bytes_per_launch": attn_bytes, "us_per_launch": attn_ms * 1e3},
+        "clocks": clocks,
+        "device_status": status,
+    }
+
+    if rank == 0 and not args.no_cpu_baseline:
+        line["cpu_baseline"], line["parity"] = cpu_baseline_and_parity(eng, q_rot[0], out[0], lengths, table)
+    if rank == 0:
+        print(json.dumps(line))
+    eng.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline_and_parity(eng, q_rot0, out0, lengths, table):
+    """CPU-baseline leg: times the oracle on a sample of layer 0 and uses its fp32 mode to check the GPU result."""
+    import torch
+
+    from oracle import qm_oracle as oracle
+
+    sample = list(range(0, BATCH, 4))
+    kview, vview = eng.pool_view(0)
+    kpool = kview.view(torch.int16).cpu().numpy().view(np.uint16)
+    vpool = vview.view(torch.int16).cpu().numpy().view(np.uint16)
+    q_bits = q_rot0.view(torch.int16).cpu().numpy().view(np.uint16)
+    out_bits = out0.view(torch.int16).cpu().numpy().view(np.uint16)
+    lens = lengths[sample] + 1
+    key_caches = [oracle.gather_paged(kpool, table[s], int(lengths[s]) + 1, int(lengths[s]) + 1) for s in sample]
+    value_caches = [oracle.gather_paged(vpool, table[s], int(lengths[s]) + 1, int(lengths[s]) + 1) for s in sample]
+    q_sample = np.ascontiguousarray(q_bits[sample])
+    seconds, _ = cpu_attention_sample(q_sample, key_caches, value_caches, lens, repeats=3)
+    sample_bytes = algorithmic_bytes_per_layer(lengths[sample])
+    want = oracle.decode_attention(q_sample, key_caches, value_caches, lens, mode="fp32")
+    metrics = oracle.error_metrics(oracle.bf16_to_f32(out_bits[sample]), want)
+    cpu = {"value": sample_bytes / seconds / 1e9, "unit": "GB/s", "cores": host_cores(), "kind": "port",
+           "sample": f"{len(sample)} of {BATCH} streams of layer 0 (every 4th), best of 3, bf16-faithful restatement "
+                     "of the reference kernels, OpenMP over (stream, kv head)",
+           "seconds": seconds}
+    parity = {"against": "fp32 oracle on the same cache bits", "streams_checked": len(sample), **metrics,
+              "tolerance": {"max_abs": 2e-2, "mean_rel": 1e-2},
+              "ok": bool(metrics["max_abs"] <= 2e-2 and metrics["mean_rel"] <= 1e-2)}
+    return cpu, parity
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

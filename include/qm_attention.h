@@ -1,0 +1,183 @@
+/*
+ * qm_attention.h - C ABI of the B200 (sm_100a) talker attention path.
+ *
+ * The reference engine (abouya9854/qingming-qwen3-tts) has no FFI: its boundary
+ * for this path is the set of private launcher methods of NativeTalkerEngine
+ * in devices/rtx4090-24g/qwen3_tts_1_7b.cu ("17.cu" below).  Every entry point
+ * here names the launcher (file:line) it stands in for.
+ *
+ * Conventions (same as the reference's kernels, 17.cu:15414-15423):
+ *   - bf16 tensors are `uint16_t*` DEVICE pointers; activations are laid out
+ *     [tokens][heads][128]; norm weights are [128].
+ *   - int arrays (positions, seq_lens, cu_seqlens, page_table) are `int32_t*`
+ *     DEVICE pointers.
+ *   - `stream` is a cudaStream_t passed as void*; every launch goes to it and
+ *     nothing is synchronised unless the comment says so.
+ *   - no function throws; each returns QM_OK (0) or a negative status, and
+ *     qm_last_error_string() describes the last failure on the calling thread.
+ *   - handles are thread-compatible: one caller at a time per handle.
+ *
+ * KV cache layout (replaces the per-layer contiguous [kv_head][max_cache][128]
+ * caches of LayerCache, 17.cu:16419-16438): per layer one K pool and one V pool
+ *     pool[page][kv_head][64][128]  bf16
+ * so that one (page, kv_head) tile is 16 KB contiguous.  Token t of stream s
+ * lives at page = page_table[s * max_pages + (t >> 6)], slot = t & 63.  K is
+ * stored after RMSNorm and RoPE, V raw (17.cu:15553-15572).
+ */
+#ifndef QM_ATTENTION_H
+#define QM_ATTENTION_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QM_OK 0
+#define QM_EINVAL (-1)     /* bad argument, detected before any launch          */
+#define QM_ECAPACITY (-2)  /* position/page beyond the pool ("cache overflow", 17.cu:17204) */
+#define QM_ECUDA (-3)      /* a CUDA runtime call or launch failed               */
+#define QM_ETIMEOUT (-4)   /* a bounded device-side wait gave up                 */
+#define QM_ENOMEM (-5)     /* device allocation failed                           */
+#define QM_EDEVICE (-6)    /* not a compute-capability 10.x device               */
+
+#define QM_HEAD_DIM 128
+#define QM_PAGE_TOKENS 64
+
+/* Device status bits written by kernels into the pool's status word. */
+#define QM_DEVSTAT_BAD_PAGE 1u   /* page id outside the pool, access skipped     */
+#define QM_DEVSTAT_BAD_POS 2u    /* position beyond max_pages * 64, skipped      */
+#define QM_DEVSTAT_TIMEOUT 4u    /* bounded mbarrier wait expired                */
+
+typedef struct qm_kv_pool qm_kv_pool;
+
+/* Text for the last non-zero status returned on this thread.  Stands in for the
+ * std::runtime_error text built by cuda_check (17.cu:17440-17453). */
+const char* qm_last_error_string(void);
+
+/* Replaces validate_rtx4090_24g_device (17.cu:7769-7804): requires compute
+ * capability 10.x and 32-wide warps; the SM count is read, not fixed.
+ * Optionally returns the SM count. */
+int32_t qm_validate_b200_device(int32_t device, int32_t* sm_count_out);
+
+/* ---- KV pool: LayerCache + allocation loop (17.cu:16419-16438, :16506-16533) */
+
+/* Allocates zero-filled K and V pools for `layers` layers of `num_pages` pages
+ * on the current device.  kv_heads in 1..64. */
+int32_t qm_kv_pool_create(int32_t layers, int32_t num_pages, int32_t kv_heads, qm_kv_pool** pool_out);
+int32_t qm_kv_pool_destroy(qm_kv_pool* pool);
+
+/* reset_request (17.cu:16607-16629): zero every page of every layer on
+ * `stream`, then synchronise that stream, as the reference does. */
+int32_t qm_kv_pool_reset(qm_kv_pool* pool, void* stream);
+
+/* Device pointers of one layer's pools (for tests and for callers that fill
+ * or snapshot the cache themselves) and the pool geometry. */
+uint16_t* qm_kv_pool_key_ptr(qm_kv_pool* pool, int32_t layer);
+uint16_t* qm_kv_pool_value_ptr(qm_kv_pool* pool, int32_t layer);
+int32_t qm_kv_pool_num_pages(const qm_kv_pool* pool);
+int32_t qm_kv_pool_kv_heads(const qm_kv_pool* pool);
+
+/* Reads and clears the device status word (QM_DEVSTAT_* bits) after
+ * synchronising `stream`.  Returns QM_OK and the bits through *bits_out. */
+int32_t qm_kv_pool_status(qm_kv_pool* pool, void* stream, uint32_t* bits_out);
+
+/* ---- RoPE table: make_talker_rope (17.cu:21758-21772) */
+
+/* Fills DEVICE arrays cosine/sine [rows][128] bf16 for positions
+ * start .. start+rows-1 with the reference's double-precision recipe.  The
+ * values are computed on the host and copied on `stream` (synchronised before
+ * return).  The reference uploads one row per decode step (17.cu:17221-17239);
+ * here the table is built once and indexed by position. */
+int32_t qm_rope_table_fill(uint16_t* cosine_dev, uint16_t* sine_dev, int32_t rows, int32_t start, double theta,
+                           void* stream);
+
+/* ---- fused QK-RMSNorm + RoPE + paged append */
+
+/* Decode step for `batch` independent streams: launch_qk_norm_rope_cache_m1
+ * (17.cu:17741-17778; kernel :15412-15574), batched and paged.
+ *   q [batch][q_heads][128], k, v [batch][kv_heads][128]  pre-norm projections
+ *   positions[batch]: position of the new token of each stream (the
+ *     reference's scalar cache_position)
+ *   rope_cos / rope_sin [rope_rows][128], row index = position
+ *   q_rot [batch][q_heads][128] receives normed+roped queries
+ * K (normed, roped) and V (raw) are written to the pool at (page, slot) of
+ * each position.  A position beyond max_pages*64 or a page id outside the pool
+ * sets a status bit and skips that row's cache write. */
+int32_t qm_decode_append_rope(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const uint16_t* k,
+                              const uint16_t* v, const uint16_t* q_norm_weight, const uint16_t* k_norm_weight,
+                              const uint16_t* rope_cos, const uint16_t* rope_sin, int32_t rope_rows,
+                              const int32_t* positions, const int32_t* page_table, int32_t max_pages,
+                              int32_t batch, int32_t q_heads, float epsilon, uint16_t* q_rot, void* stream);
+
+/* Prefill, packed varlen: the launch_rmsnorm x2 + launch_rope_rows x2 +
+ * scatter_prefill_cache sequence of prefill() (17.cu:16763-16798) in one
+ * kernel.  Sequence s owns packed rows cu_seqlens[s] .. cu_seqlens[s+1]-1 and
+ * its first row has position start_positions[s] (NULL = all zero, as in the
+ * reference where prefill starts an empty cache).  total_tokens is
+ * cu_seqlens[batch] as known to the host. */
+int32_t qm_prefill_append_rope_varlen(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const uint16_t* k,
+                                      const uint16_t* v, const uint16_t* q_norm_weight,
+                                      const uint16_t* k_norm_weight, const uint16_t* rope_cos,
+                                      const uint16_t* rope_sin, int32_t rope_rows, const int32_t* cu_seqlens,
+                                      const int32_t* start_positions, const int32_t* page_table,
+                                      int32_t max_pages, int32_t batch, int32_t total_tokens, int32_t q_heads,
+                                      float epsilon, uint16_t* q_rot, void* stream);
+
+/* ---- decode attention: launch_attention with query_length == 1
+ *      (17.cu:17895-17952; kernel talker_attention_gqa2_m1_locality_kernel :16061-16251) */
+
+/* Bytes of caller-owned scratch qm_decode_attention needs for a batch. */
+int64_t qm_decode_workspace_bytes(int32_t batch, int32_t kv_heads);
+
+/* Split-KV flash decoding over the paged cache, q_heads == 2 * kv_heads.
+ *   q_rot [batch][q_heads][128]: output of qm_decode_append_rope
+ *   seq_lens[batch]: number of keys each stream attends, i.e. position + 1
+ *     (the appended token is included, 17.cu:16080); 0 gives a zero row
+ *   out [batch][q_heads][128] bf16, the reference's `context`
+ * Softmax scale is 1/sqrtf(128) (17.cu:17910-17914).  Scores, softmax and the
+ * PV sum stay in fp32; the result is rounded to bf16 once.  Deterministic:
+ * the split of keys over CTAs depends only on seq_lens and the SM count. */
+int32_t qm_decode_attention(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const int32_t* seq_lens,
+                            const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads,
+                            uint16_t* out, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Same, but stops before normalisation and returns the partial softmax state
+ * of each (stream, query head) over the keys held in THIS pool:
+ *   partial [batch][q_heads][130] fp32 = { m (max scaled score, natural-log
+ *   domain), l (sum of exp(s - m)), o[128] (unnormalised) }.
+ * Used when one stream's keys are split over several GPUs: each GPU calls this
+ * on its slice, the partials are exchanged (33 280 B per rank for 4 streams),
+ * and qm_attention_combine finishes.  A stream with seq_len 0 yields
+ * m = -inf, l = 0, o = 0. */
+int32_t qm_decode_attention_partial(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot,
+                                    const int32_t* seq_lens, const int32_t* page_table, int32_t max_pages,
+                                    int32_t batch, int32_t q_heads, float* partial, void* workspace,
+                                    int64_t workspace_bytes, void* stream);
+
+/* Log-sum-exp combine of `parts` partial states per row:
+ *   partials [parts][rows][130] fp32, out [rows][128] bf16,
+ *   out = sum_g e^{m_g - M} o_g / sum_g e^{m_g - M} l_g,  M = max_g m_g.
+ * Parts are folded in index order, so the result does not depend on timing. */
+int32_t qm_attention_combine(const float* partials, int32_t parts, int32_t rows, uint16_t* out, void* stream);
+
+/* ---- prefill attention: launch_attention with query_length > 1
+ *      (17.cu:17954-17985; kernel talker_attention_kernel :15791-16054) */
+
+/* Causal GQA attention over packed varlen queries whose keys are already in
+ * the paged cache (the reference also attends over the cache it has just
+ * scattered, 17.cu:16791-16807).  Row i of sequence s (position
+ * start_positions[s] + i) attends keys 0 .. start_positions[s] + i.
+ *   q_rot, out [total_tokens][q_heads][128] bf16
+ * max_seqlen: the longest sequence, as known to the host (sizes the grid).
+ * tcgen05 tensor-core kernel with TMEM accumulators; fp32 softmax. */
+int32_t qm_prefill_attention_varlen(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot,
+                                    const int32_t* cu_seqlens, const int32_t* start_positions,
+                                    const int32_t* page_table, int32_t max_pages, int32_t batch,
+                                    int32_t total_tokens, int32_t max_seqlen, int32_t q_heads, uint16_t* out,
+                                    void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QM_ATTENTION_H */

@@ -1,0 +1,253 @@
+"""numpy front end of the CPU oracle (oracle/qm_oracle.c) and of the optional
+reference-kernel harness (oracle/_ref/libqm_refkernels.so).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
+benchmark's CPU-baseline leg, never by the library under test.
+
+bf16 tensors are numpy uint16 arrays holding the raw bits.
+"""
+from __future__ import annotations
+
+import ctypes
+import subprocess
+from ctypes import POINTER, c_double, c_float, c_int, c_int32, c_int64, c_uint16, c_uint64, c_void_p
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+LIB = HERE / "libqm_oracle.so"
+REF_LIB = HERE / "_ref" / "libqm_refkernels.so"
+D = 128
+PAGE = 64
+
+_lib = None
+_ref = None
+
+
+def build(with_reference: bool = False) -> None:
+    """Compiles the C restatement (and, where the reference checkout exists, the harness)."""
+    subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
+    if with_reference and Path("/root/reference/devices/rtx4090-24g/qwen3_tts_1_7b.cu").exists():
+        subprocess.run(["make", "-C", str(HERE), "ref"], check=True, capture_output=True)
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB.exists():
+            build()
+        _lib = ctypes.CDLL(str(LIB))
+        _lib.qmo_f32_to_bf16.restype = c_uint16
+        _lib.qmo_f32_to_bf16.argtypes = [c_float]
+        _lib.qmo_bf16_to_f32.restype = c_float
+        _lib.qmo_bf16_to_f32.argtypes = [c_uint16]
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(c_void_p) if a is not None else None
+
+
+def _u16(a):
+    a = np.ascontiguousarray(a)
+    assert a.dtype == np.uint16
+    return a
+
+
+# ------------------------------------------------------------------ helpers
+
+def bf16_to_f32(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    lib().qmo_f32_to_bf16_array(_p(x), _p(out), c_int64(x.size))
+    return out
+
+
+def normal_bf16(seed: int, shape) -> np.ndarray:
+    """N(0,1) bf16 tensor drawn in row-major order from SplitMix64(seed) by Box-Muller."""
+    out = np.empty(shape, dtype=np.uint16)
+    lib().qmo_fill_normal_bf16(c_uint64(seed), _p(out), c_int64(out.size))
+    return out
+
+
+def uniform_int(seed: int, lo: int, hi: int, n: int) -> np.ndarray:
+    out = np.empty(n, dtype=np.int32)
+    lib().qmo_fill_uniform_int(c_uint64(seed), c_int32(lo), c_int32(hi), _p(out), c_int64(n))
+    return out
+
+
+def shuffled_range(seed: int, n: int) -> np.ndarray:
+    out = np.empty(n, dtype=np.int32)
+    lib().qmo_shuffled_range(c_uint64(seed), _p(out), c_int64(n))
+    return out
+
+
+def make_rope(rows: int, start: int = 0, theta: float = 1.0e6):
+    cos = np.empty((rows, D), dtype=np.uint16)
+    sin = np.empty((rows, D), dtype=np.uint16)
+    lib().qmo_make_rope(c_int(rows), c_int(start), c_double(theta), _p(cos), _p(sin))
+    return cos, sin
+
+
+# ------------------------------------------------------------- path pieces
+
+def append(q, k, v, q_w, k_w, cos_rows, sin_rows, first_pos, key_cache, value_cache, eps=1.0e-6):
+    """Norm + RoPE + append of `tokens` consecutive positions of one sequence.
+
+    q [tokens][Hq][128], k/v [tokens][Hkv][128]; cos_rows/sin_rows [tokens][128] for those positions;
+    caches [Hkv][max_cache][128] updated in place.  Returns q_rot.
+    """
+    q, k, v = _u16(q), _u16(k), _u16(v)
+    tokens, hq = q.shape[0], q.shape[1]
+    hkv, max_cache = key_cache.shape[0], key_cache.shape[1]
+    q_rot = np.empty_like(q)
+    lib().qmo_append(_p(q), _p(k), _p(v), _p(_u16(q_w)), _p(_u16(k_w)), _p(_u16(cos_rows)), _p(_u16(sin_rows)),
+                     c_float(eps), c_int(tokens), c_int(first_pos), c_int(hq), c_int(hkv), c_int(max_cache),
+                     _p(q_rot), _p(key_cache), _p(value_cache))
+    return q_rot
+
+
+def decode_attention(q_rot, key_caches, value_caches, key_lens, mode="fp32"):
+    """Batched decode attention.  q_rot [B][Hq][128]; caches: lists of [Hkv][max_cache][128] arrays.
+
+    mode "ref" -> uint16 bf16 bits, "fp32" -> float32.
+    """
+    q_rot = _u16(q_rot)
+    b, hq = q_rot.shape[0], q_rot.shape[1]
+    hkv = key_caches[0].shape[0]
+    kp = (c_void_p * b)(*[kc.ctypes.data for kc in key_caches])
+    vp = (c_void_p * b)(*[vc.ctypes.data for vc in value_caches])
+    maxc = np.array([kc.shape[1] for kc in key_caches], dtype=np.int32)
+    lens = np.ascontiguousarray(key_lens, dtype=np.int32)
+    out16 = np.empty((b, hq, D), dtype=np.uint16) if mode == "ref" else None
+    out32 = np.empty((b, hq, D), dtype=np.float32) if mode != "ref" else None
+    rc = lib().qmo_decode_attention_batch(_p(q_rot), kp, vp, _p(maxc), _p(lens), c_int(b), c_int(hq), c_int(hkv),
+                                          c_int(0 if mode == "ref" else 1), _p(out16), _p(out32))
+    assert rc == 0
+    return out16 if mode == "ref" else out32
+
+
+def prefill_attention(q_rot, key_cache, value_cache, seq, cache_before=0, rows=None, mode="fp32"):
+    """Causal attention of one sequence over its cache.  rows=(begin,end) restricts the computed rows;
+    the other rows of the result are left zero."""
+    q_rot = _u16(q_rot)
+    hq = q_rot.shape[1]
+    hkv, max_cache = key_cache.shape[0], key_cache.shape[1]
+    begin, end = rows if rows is not None else (0, seq)
+    out16 = np.zeros((seq, hq, D), dtype=np.uint16) if mode == "ref" else None
+    out32 = np.zeros((seq, hq, D), dtype=np.float32) if mode != "ref" else None
+    rc = lib().qmo_prefill_attention(_p(q_rot), _p(key_cache), _p(value_cache), c_int(max_cache), c_int(seq),
+                                     c_int(cache_before), c_int(hq), c_int(hkv), c_int(begin), c_int(end),
+                                     c_int(0 if mode == "ref" else 1), _p(out16), _p(out32))
+    assert rc == 0
+    return out16 if mode == "ref" else out32
+
+
+def attention_partial(q_row, key_cache, value_cache, kv_head, key_begin, key_end):
+    m = c_float()
+    l = c_float()
+    o = np.empty(D, dtype=np.float32)
+    lib().qmo_attention_partial(_p(_u16(q_row)), _p(key_cache), _p(value_cache), c_int(kv_head),
+                                c_int(key_cache.shape[1]), c_int(key_begin), c_int(key_end), ctypes.byref(m),
+                                ctypes.byref(l), _p(o))
+    return m.value, l.value, o
+
+
+def combine_partials(m, l, o):
+    m = np.ascontiguousarray(m, dtype=np.float32)
+    l = np.ascontiguousarray(l, dtype=np.float32)
+    o = np.ascontiguousarray(o, dtype=np.float32)
+    out = np.empty(D, dtype=np.float32)
+    lib().qmo_combine_partials(_p(m), _p(l), _p(o), c_int(m.size), _p(out))
+    return out
+
+
+def gather_paged(pool, page_row, tokens, max_cache):
+    """pool [pages][Hkv][64][128] -> contiguous [Hkv][max_cache][128] for one stream."""
+    pool = _u16(pool)
+    hkv = pool.shape[1]
+    out = np.zeros((hkv, max_cache, D), dtype=np.uint16)
+    row = np.ascontiguousarray(page_row, dtype=np.int32)
+    lib().qmo_gather_paged(_p(pool), _p(row), c_int(tokens), c_int(hkv), c_int(PAGE), c_int(max_cache), _p(out))
+    return out
+
+
+def scatter_paged(cache, page_row, tokens, pool):
+    cache = _u16(cache)
+    row = np.ascontiguousarray(page_row, dtype=np.int32)
+    lib().qmo_scatter_paged(_p(cache), _p(row), c_int(tokens), c_int(cache.shape[0]), c_int(PAGE),
+                            c_int(cache.shape[1]), _p(pool))
+
+
+# ------------------------------------------------------------ error metrics
+
+def error_metrics(got_f32: np.ndarray, want_f32: np.ndarray) -> dict:
+    """max-abs, aggregate relative (sum|a-b| / sum|b|) and element-wise mean relative error."""
+    diff = np.abs(got_f32.astype(np.float64) - want_f32.astype(np.float64))
+    return {
+        "max_abs": float(diff.max()) if diff.size else 0.0,
+        "mean_rel": float(diff.sum() / max(np.abs(want_f32).astype(np.float64).sum(), 1e-30)),
+        "mean_rel_elementwise": float((diff / np.maximum(np.abs(want_f32), 1e-3)).mean()) if diff.size else 0.0,
+    }
+
+
+# ------------------------------------------- reference kernels (GPU, optional)
+
+def ref_available() -> bool:
+    return REF_LIB.exists()
+
+
+def ref() -> ctypes.CDLL:
+    """The reference's own CUDA kernels behind the harness; needs a GPU to call."""
+    global _ref
+    if _ref is None:
+        _ref = ctypes.CDLL(str(REF_LIB))
+    return _ref
+
+
+def ref_decode_append(q, k, v, q_w, k_w, cos_row, sin_row, key_cache, value_cache, position):
+    q, k, v = _u16(q), _u16(k), _u16(v)
+    q_rot = np.empty_like(q)
+    rc = ref().qmref_decode_append(_p(q), _p(k), _p(v), _p(_u16(q_w)), _p(_u16(k_w)), _p(_u16(cos_row)),
+                                   _p(_u16(sin_row)), _p(q_rot), _p(key_cache), _p(value_cache), c_int(q.shape[0]),
+                                   c_int(k.shape[0]), c_int(key_cache.shape[1]), c_int(position))
+    assert rc == 0, rc
+    return q_rot
+
+
+def ref_prefill_append(q, k, v, q_w, k_w, cos_rows, sin_rows, key_cache, value_cache):
+    q, k, v = _u16(q), _u16(k), _u16(v)
+    q_rot = np.empty_like(q)
+    rc = ref().qmref_prefill_append(_p(q), _p(k), _p(v), _p(_u16(q_w)), _p(_u16(k_w)), _p(_u16(cos_rows)),
+                                    _p(_u16(sin_rows)), _p(q_rot), _p(key_cache), _p(value_cache), c_int(q.shape[0]),
+                                    c_int(q.shape[1]), c_int(k.shape[1]), c_int(key_cache.shape[1]))
+    assert rc == 0, rc
+    return q_rot
+
+
+def ref_attention(q_rot, key_cache, value_cache, query_length, cache_before, iterations=1):
+    """Returns (context bits, mean ms per launch); context is None when the reference's launcher
+    would need more than its 48 KB of dynamic shared memory."""
+    q_rot = _u16(q_rot)
+    hq = q_rot.shape[-2]
+    out = np.empty_like(q_rot)
+    ms = c_float()
+    rc = ref().qmref_attention(_p(q_rot), _p(key_cache), _p(value_cache), _p(out), c_int(query_length),
+                               c_int(cache_before), c_int(hq), c_int(key_cache.shape[0]), c_int(key_cache.shape[1]),
+                               c_int(iterations), ctypes.byref(ms))
+    if rc == -2:
+        return None, None
+    assert rc == 0, rc
+    return out, ms.value
+
+
+def ref_make_rope(rows, start=0):
+    cos = np.empty((rows, D), dtype=np.uint16)
+    sin = np.empty((rows, D), dtype=np.uint16)
+    ref().qmref_make_rope(c_int(rows), c_int(start), _p(cos), _p(sin))
+    return cos, sin

@@ -1,0 +1,209 @@
+// Include-only harness around the reference engine's own device kernels.
+//
+// TEST INFRASTRUCTURE ONLY: nothing in the shipped library links or loads it.
+// It compiles the reference's 1.7B translation unit unmodified, from where it
+// lies in the reference checkout (REFERENCE_DIR on the nvcc command line), and
+// exposes plain C entry points that launch the reference's talker kernels with
+// host buffers.  No reference source is copied: the only reference text here
+// is the names of the symbols being called.
+//
+// Built by oracle/Makefile into oracle/_ref/libqm_refkernels.so.  Used to
+//   * pin the C restatement (oracle/qm_oracle.c) against the reference's real
+//     output bits on the same inputs,
+//   * produce the golden fixtures under tests/golden/,
+//   * time the reference's kernels on the same GPU for the report.
+//
+// Kernels launched (devices/rtx4090-24g/qwen3_tts_1_7b.cu):
+//   talker_qk_norm_rope_cache_fused_kernel    :15412   launcher :17741
+//   talker_attention_gqa2_m1_locality_kernel  :16061   dispatch :17916
+//   talker_attention_kernel                   :15791   dispatch :17954
+//   talker_rope_rows_kernel                   :15578   launcher :17780
+//   talker_scatter_prefill_kv_kernel          :15677   launcher :17818
+//   code_predictor::rmsnorm_kernel            :8295    launcher :8927
+// Launch shapes and shared-memory sizes follow the cited launchers.
+
+#define main qm_refharness_unused_reference_main
+#include "devices/rtx4090-24g/qwen3_tts_1_7b.cu"
+#undef main
+
+#include <cstdint>
+#include <cstring>
+
+namespace {
+
+namespace rt = qwen3_tts::baseline::talker;
+namespace rp = qwen3_tts::baseline::code_predictor;
+
+struct DevBuf {
+    void* p = nullptr;
+    size_t bytes = 0;
+    cudaError_t alloc(size_t n) {
+        bytes = n;
+        return cudaMalloc(&p, n ? n : 1);
+    }
+    ~DevBuf() {
+        if (p) cudaFree(p);
+    }
+    template <class T>
+    T* as() {
+        return static_cast<T*>(p);
+    }
+};
+
+#define RH_CHECK(expr)                                   \
+    do {                                                 \
+        cudaError_t rh_status = (expr);                  \
+        if (rh_status != cudaSuccess) return (int)rh_status; \
+    } while (0)
+
+constexpr int kD = 128;
+
+}  // namespace
+
+extern "C" {
+
+// Decode: fused per-head RMSNorm + RoPE; K heads also append K (roped) and V
+// (raw) at cache_position.  Caches are host arrays [kv_heads][max_cache][128],
+// updated in place.  cosine/sine: the 128-entry row of that position.
+int qmref_decode_append(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* q_norm_w,
+                        const uint16_t* k_norm_w, const uint16_t* cosine, const uint16_t* sine, uint16_t* q_rot,
+                        uint16_t* key_cache, uint16_t* value_cache, int q_heads, int kv_heads, int max_cache,
+                        int cache_position) {
+    const size_t qb = (size_t)q_heads * kD * 2, kb = (size_t)kv_heads * kD * 2;
+    const size_t cb = (size_t)kv_heads * max_cache * kD * 2;
+    DevBuf dq, dk, dv, dqw, dkw, dc, ds, dqr, dkc, dvc;
+    RH_CHECK(dq.alloc(qb)); RH_CHECK(dk.alloc(kb)); RH_CHECK(dv.alloc(kb));
+    RH_CHECK(dqw.alloc(kD * 2)); RH_CHECK(dkw.alloc(kD * 2)); RH_CHECK(dc.alloc(kD * 2)); RH_CHECK(ds.alloc(kD * 2));
+    RH_CHECK(dqr.alloc(qb)); RH_CHECK(dkc.alloc(cb)); RH_CHECK(dvc.alloc(cb));
+    RH_CHECK(cudaMemcpy(dq.p, q, qb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dk.p, k, kb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dv.p, v, kb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dqw.p, q_norm_w, kD * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dkw.p, k_norm_w, kD * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dc.p, cosine, kD * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(ds.p, sine, kD * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dkc.p, key_cache, cb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dvc.p, value_cache, cb, cudaMemcpyHostToDevice));
+    QINGMING_CUDA_LAUNCH(rt::talker_qk_norm_rope_cache_fused_kernel, dim3((unsigned)(q_heads + kv_heads)), dim3(128), 0,
+                         (cudaStream_t) nullptr, dq.as<uint16_t>(), dk.as<uint16_t>(), dv.as<uint16_t>(),
+                         dqw.as<uint16_t>(), dkw.as<uint16_t>(), dc.as<uint16_t>(), ds.as<uint16_t>(),
+                         dqr.as<uint16_t>(), dkc.as<uint16_t>(), dvc.as<uint16_t>(), q_heads, kv_heads, kD, max_cache,
+                         cache_position, 1.0e-6f);
+    RH_CHECK(cudaGetLastError());
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(q_rot, dqr.p, qb, cudaMemcpyDeviceToHost));
+    RH_CHECK(cudaMemcpy(key_cache, dkc.p, cb, cudaMemcpyDeviceToHost));
+    RH_CHECK(cudaMemcpy(value_cache, dvc.p, cb, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+// Prefill spelling of the same math: rmsnorm(q), rmsnorm(k), rope(q), rope(k),
+// scatter into the cache rows 0..seq-1.  cosine/sine [seq][128].
+int qmref_prefill_append(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* q_norm_w,
+                         const uint16_t* k_norm_w, const uint16_t* cosine, const uint16_t* sine, uint16_t* q_rot,
+                         uint16_t* key_cache, uint16_t* value_cache, int seq, int q_heads, int kv_heads,
+                         int max_cache) {
+    const size_t qb = (size_t)seq * q_heads * kD * 2, kb = (size_t)seq * kv_heads * kD * 2;
+    const size_t cb = (size_t)kv_heads * max_cache * kD * 2, rb = (size_t)seq * kD * 2;
+    DevBuf dq, dk, dv, dqw, dkw, dc, ds, dqn, dkn, dqr, dkr, dkc, dvc;
+    RH_CHECK(dq.alloc(qb)); RH_CHECK(dk.alloc(kb)); RH_CHECK(dv.alloc(kb));
+    RH_CHECK(dqw.alloc(kD * 2)); RH_CHECK(dkw.alloc(kD * 2)); RH_CHECK(dc.alloc(rb)); RH_CHECK(ds.alloc(rb));
+    RH_CHECK(dqn.alloc(qb)); RH_CHECK(dkn.alloc(kb)); RH_CHECK(dqr.alloc(qb)); RH_CHECK(dkr.alloc(kb));
+    RH_CHECK(dkc.alloc(cb)); RH_CHECK(dvc.alloc(cb));
+    RH_CHECK(cudaMemcpy(dq.p, q, qb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dk.p, k, kb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dv.p, v, kb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dqw.p, q_norm_w, kD * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dkw.p, k_norm_w, kD * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dc.p, cosine, rb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(ds.p, sine, rb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dkc.p, key_cache, cb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dvc.p, value_cache, cb, cudaMemcpyHostToDevice));
+    rp::launch_rmsnorm(dq.as<uint16_t>(), dqw.as<uint16_t>(), dqn.as<uint16_t>(), seq * q_heads, kD, nullptr);
+    rp::launch_rmsnorm(dk.as<uint16_t>(), dkw.as<uint16_t>(), dkn.as<uint16_t>(), seq * kv_heads, kD, nullptr);
+    {
+        const uint64_t count = (uint64_t)seq * q_heads * kD;
+        QINGMING_CUDA_LAUNCH(rt::talker_rope_rows_kernel, dim3((unsigned)((count + 255) / 256)), dim3(256), 0,
+                             (cudaStream_t) nullptr, dqn.as<uint16_t>(), dc.as<uint16_t>(), ds.as<uint16_t>(),
+                             dqr.as<uint16_t>(), seq, q_heads, kD);
+        RH_CHECK(cudaGetLastError());
+    }
+    {
+        const uint64_t count = (uint64_t)seq * kv_heads * kD;
+        QINGMING_CUDA_LAUNCH(rt::talker_rope_rows_kernel, dim3((unsigned)((count + 255) / 256)), dim3(256), 0,
+                             (cudaStream_t) nullptr, dkn.as<uint16_t>(), dc.as<uint16_t>(), ds.as<uint16_t>(),
+                             dkr.as<uint16_t>(), seq, kv_heads, kD);
+        RH_CHECK(cudaGetLastError());
+        QINGMING_CUDA_LAUNCH(rt::talker_scatter_prefill_kv_kernel, dim3((unsigned)((count + 255) / 256)), dim3(256), 0,
+                             (cudaStream_t) nullptr, dkr.as<uint16_t>(), dv.as<uint16_t>(), dkc.as<uint16_t>(),
+                             dvc.as<uint16_t>(), seq, kv_heads, kD, max_cache);
+        RH_CHECK(cudaGetLastError());
+    }
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(q_rot, dqr.p, qb, cudaMemcpyDeviceToHost));
+    RH_CHECK(cudaMemcpy(key_cache, dkc.p, cb, cudaMemcpyDeviceToHost));
+    RH_CHECK(cudaMemcpy(value_cache, dvc.p, cb, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+// Attention over a cache that already holds keys 0..cache_before+query_length-1.
+// query_length == 1 with q_heads == 2*kv_heads takes the GQA-2 M=1 kernel,
+// anything else the generic one, exactly as the reference dispatcher does.
+// iterations > 1 repeats the launch and reports the mean milliseconds per
+// launch through *mean_ms (device time, CUDA events).  Returns a cudaError_t
+// value, or -2 when the dynamic shared memory the launcher would request
+// exceeds the 48 KB the reference never raises.
+int qmref_attention(const uint16_t* q_rot, const uint16_t* key_cache, const uint16_t* value_cache, uint16_t* context,
+                    int query_length, int cache_before, int q_heads, int kv_heads, int max_cache, int iterations,
+                    float* mean_ms) {
+    const size_t qb = (size_t)query_length * q_heads * kD * 2;
+    const size_t cb = (size_t)kv_heads * max_cache * kD * 2;
+    const int max_key_len = cache_before + query_length;
+    const float scale = 1.0f / std::sqrt((float)kD);
+    const bool gqa2 = query_length == 1 && q_heads == 2 * kv_heads;
+    const size_t shared = gqa2 ? (size_t)(2 * kD + 2 * max_key_len) * 2 : (size_t)(kD + max_key_len) * 2;
+    if (shared > 48 * 1024) return -2;
+    DevBuf dq, dkc, dvc, dctx;
+    RH_CHECK(dq.alloc(qb)); RH_CHECK(dkc.alloc(cb)); RH_CHECK(dvc.alloc(cb)); RH_CHECK(dctx.alloc(qb));
+    RH_CHECK(cudaMemcpy(dq.p, q_rot, qb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dkc.p, key_cache, cb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dvc.p, value_cache, cb, cudaMemcpyHostToDevice));
+    cudaEvent_t e0, e1;
+    RH_CHECK(cudaEventCreate(&e0));
+    RH_CHECK(cudaEventCreate(&e1));
+    if (iterations < 1) iterations = 1;
+    for (int it = -1; it < iterations; ++it) {
+        if (it == 0) RH_CHECK(cudaEventRecord(e0, nullptr));
+        if (gqa2) {
+            QINGMING_CUDA_LAUNCH(rt::talker_attention_gqa2_m1_locality_kernel, dim3((unsigned)kv_heads), dim3(256),
+                                 shared, (cudaStream_t) nullptr, dq.as<uint16_t>(), dkc.as<uint16_t>(),
+                                 dvc.as<uint16_t>(), dctx.as<uint16_t>(), cache_before, q_heads, kv_heads, kD,
+                                 max_cache, -1, scale);
+        } else {
+            QINGMING_CUDA_LAUNCH(rt::talker_attention_kernel, dim3((unsigned)(q_heads * query_length)), dim3(256),
+                                 shared, (cudaStream_t) nullptr, dq.as<uint16_t>(), dkc.as<uint16_t>(),
+                                 dvc.as<uint16_t>(), dctx.as<uint16_t>(), query_length, cache_before, q_heads,
+                                 kv_heads, kD, max_cache, -1, scale);
+        }
+        RH_CHECK(cudaGetLastError());
+    }
+    RH_CHECK(cudaEventRecord(e1, nullptr));
+    RH_CHECK(cudaDeviceSynchronize());
+    float ms = 0.0f;
+    RH_CHECK(cudaEventElapsedTime(&ms, e0, e1));
+    if (mean_ms) *mean_ms = ms / (float)iterations;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    RH_CHECK(cudaMemcpy(context, dctx.p, qb, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+// Host RoPE table exactly as the engine builds it.
+int qmref_make_rope(int rows, int start, uint16_t* cosine, uint16_t* sine) {
+    auto r = qwen3_tts::baseline::make_talker_rope(rows, start);
+    std::memcpy(cosine, r.cos.data(), r.cos.size() * 2);
+    std::memcpy(sine, r.sin.data(), r.sin.size() * 2);
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,281 @@
+"""B200-native talker attention path of the Qwen3-TTS engine.
+
+This package holds the CUDA sources (``csrc/``), the build step and a thin
+ctypes binding of the C ABI declared in ``include/qm_attention.h``.  The
+binding exists for the tests and the benchmark: device memory and streams come
+from PyTorch, every computation goes through the C entry points.  There is no
+CPU path: if the shared library is missing or cannot be loaded, importing the
+binding raises.
+
+``TalkerAttention`` mirrors, method for method, the launcher surface of the
+reference's ``NativeTalkerEngine`` for this path
+(devices/rtx4090-24g/qwen3_tts_1_7b.cu):
+
+    launch_qk_norm_rope_cache_m1   :17741    -> qm_decode_append_rope
+    launch_attention               :17895    -> qm_decode_attention / qm_prefill_attention_varlen
+    launch_rmsnorm x2 + launch_rope_rows x2 + scatter_prefill_cache
+                                   :16763-16798 -> qm_prefill_append_rope_varlen
+    reset_request                  :16607    -> qm_kv_pool_reset
+    LayerCache                     :16419    -> qm_kv_pool_create
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_char_p, c_double, c_float, c_int32, c_int64, c_uint32, c_void_p
+
+from ._build import LIB_PATH, build_library
+
+QM_OK = 0
+QM_EINVAL = -1
+QM_ECAPACITY = -2
+QM_ECUDA = -3
+QM_ETIMEOUT = -4
+QM_ENOMEM = -5
+QM_EDEVICE = -6
+
+DEVSTAT_BAD_PAGE = 1
+DEVSTAT_BAD_POS = 2
+DEVSTAT_TIMEOUT = 4
+
+HEAD_DIM = 128
+PAGE_TOKENS = 64
+PARTIAL_STRIDE = HEAD_DIM + 2
+
+# name -> (restype, argtypes); must list every symbol of include/qm_attention.h
+ABI = {
+    "qm_last_error_string": (c_char_p, []),
+    "qm_validate_b200_device": (c_int32, [c_int32, POINTER(c_int32)]),
+    "qm_kv_pool_create": (c_int32, [c_int32, c_int32, c_int32, POINTER(c_void_p)]),
+    "qm_kv_pool_destroy": (c_int32, [c_void_p]),
+    "qm_kv_pool_reset": (c_int32, [c_void_p, c_void_p]),
+    "qm_kv_pool_key_ptr": (c_void_p, [c_void_p, c_int32]),
+    "qm_kv_pool_value_ptr": (c_void_p, [c_void_p, c_int32]),
+    "qm_kv_pool_num_pages": (c_int32, [c_void_p]),
+    "qm_kv_pool_kv_heads": (c_int32, [c_void_p]),
+    "qm_kv_pool_status": (c_int32, [c_void_p, c_void_p, POINTER(c_uint32)]),
+    "qm_rope_table_fill": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_double, c_void_p]),
+    "qm_decode_append_rope": (c_int32, [c_void_p, c_int32] + [c_void_p] * 7 + [c_int32, c_void_p, c_void_p, c_int32,
+                                                                           c_int32, c_int32, c_float, c_void_p, c_void_p]),
+    "qm_prefill_append_rope_varlen": (c_int32, [c_void_p, c_int32] + [c_void_p] * 7 +
+                                      [c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+                                       c_float, c_void_p, c_void_p]),
+    "qm_decode_workspace_bytes": (c_int64, [c_int32, c_int32]),
+    "qm_decode_attention": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
+                                      c_void_p, c_void_p, c_int64, c_void_p]),
+    "qm_decode_attention_partial": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
+                                              c_int32, c_void_p, c_void_p, c_int64, c_void_p]),
+    "qm_attention_combine": (c_int32, [c_void_p, c_int32, c_int32, c_void_p, c_void_p]),
+    "qm_prefill_attention_varlen": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
+                                              c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
+}
+
+_lib = None
+
+
+class QmError(RuntimeError):
+    """Raised when a C entry point returns a non-zero status (the reference throws std::runtime_error)."""
+
+    def __init__(self, code: int, text: str):
+        super().__init__(f"qm status {code}: {text}")
+        self.code = code
+
+
+def load_library(path=None) -> ctypes.CDLL:
+    """Loads libqm_attention_b200.so and declares every prototype.  Fails loudly when it is absent."""
+    global _lib
+    if _lib is not None and path is None:
+        return _lib
+    lib_path = str(path or LIB_PATH)
+    try:
+        lib = ctypes.CDLL(lib_path)
+    except OSError as exc:
+        raise RuntimeError(
+            f"cannot load {lib_path}: {exc}. Build it with __graft_entry__.build(); there is no CPU fallback."
+        ) from exc
+    for name, (restype, argtypes) in ABI.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    if path is None:
+        _lib = lib
+    return lib
+
+
+def _check(code: int) -> None:
+    if code != QM_OK:
+        text = load_library().qm_last_error_string()
+        raise QmError(code, text.decode() if text else "")
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    import torch
+
+    return torch.cuda.current_stream().cuda_stream
+
+
+class TalkerAttention:
+    """Owns a paged KV pool and a RoPE table on the current CUDA device and launches the attention path.
+
+    Tensors are torch CUDA tensors: bf16 activations as torch.bfloat16, integer arrays as torch.int32.
+    """
+
+    def __init__(self, layers: int, num_pages: int, q_heads: int = 16, kv_heads: int = 8, max_positions: int = 8192,
+                 theta: float = 1.0e6, epsilon: float = 1.0e-6):
+        import torch
+
+        self.lib = load_library()
+        self.layers, self.num_pages = layers, num_pages
+        self.q_heads, self.kv_heads = q_heads, kv_heads
+        self.epsilon = epsilon
+        self.max_positions = max_positions
+        handle = c_void_p()
+        _check(self.lib.qm_kv_pool_create(layers, num_pages, kv_heads, ctypes.byref(handle)))
+        self.pool = handle
+        self.rope_cos = torch.empty((max_positions, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
+        self.rope_sin = torch.empty_like(self.rope_cos)
+        _check(self.lib.qm_rope_table_fill(_ptr(self.rope_cos), _ptr(self.rope_sin), max_positions, 0, theta, _stream()))
+        self._workspace = None
+
+    def close(self) -> None:
+        if getattr(self, "pool", None):
+            self.lib.qm_kv_pool_destroy(self.pool)
+            self.pool = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- cache object ------------------------------------------------------
+    def max_cache(self, max_pages: int) -> int:
+        """Tokens one stream can hold with `max_pages` page-table entries (the reference's max_cache())."""
+        return max_pages * PAGE_TOKENS
+
+    def reset_request(self) -> None:
+        _check(self.lib.qm_kv_pool_reset(self.pool, _stream()))
+
+    def status(self) -> int:
+        bits = c_uint32()
+        _check(self.lib.qm_kv_pool_status(self.pool, _stream(), ctypes.byref(bits)))
+        return bits.value
+
+    def pool_view(self, layer: int):
+        """(K, V) torch views [num_pages][kv_heads][64][128] of one layer's pools (no copy)."""
+        import torch
+
+        shape = (self.num_pages, self.kv_heads, PAGE_TOKENS, HEAD_DIM)
+        return tuple(_wrap_device_pointer(p, shape, torch.bfloat16)
+                     for p in (self.lib.qm_kv_pool_key_ptr(self.pool, layer),
+                               self.lib.qm_kv_pool_value_ptr(self.pool, layer)))
+
+    # -- launchers ----------------------------------------------------------
+    def launch_qk_norm_rope_cache_m1(self, layer, q, k, v, q_norm_weight, k_norm_weight, positions, page_table,
+                                     q_rot=None):
+        import torch
+
+        batch = q.shape[0]
+        if q_rot is None:
+            q_rot = torch.empty_like(q)
+        _check(self.lib.qm_decode_append_rope(
+            self.pool, layer, _ptr(q), _ptr(k), _ptr(v), _ptr(q_norm_weight), _ptr(k_norm_weight),
+            _ptr(self.rope_cos), _ptr(self.rope_sin), self.max_positions, _ptr(positions), _ptr(page_table),
+            page_table.shape[1], batch, self.q_heads, self.epsilon, _ptr(q_rot), _stream()))
+        return q_rot
+
+    def prefill_norm_rope_scatter(self, layer, q, k, v, q_norm_weight, k_norm_weight, cu_seqlens, page_table,
+                                  start_positions=None, q_rot=None):
+        import torch
+
+        total = q.shape[0]
+        batch = cu_seqlens.shape[0] - 1
+        if q_rot is None:
+            q_rot = torch.empty_like(q)
+        _check(self.lib.qm_prefill_append_rope_varlen(
+            self.pool, layer, _ptr(q), _ptr(k), _ptr(v), _ptr(q_norm_weight), _ptr(k_norm_weight),
+            _ptr(self.rope_cos), _ptr(self.rope_sin), self.max_positions, _ptr(cu_seqlens), _ptr(start_positions),
+            _ptr(page_table), page_table.shape[1], batch, total, self.q_heads, self.epsilon, _ptr(q_rot), _stream()))
+        return q_rot
+
+    def workspace(self, batch: int):
+        import torch
+
+        need = self.lib.qm_decode_workspace_bytes(batch, self.kv_heads)
+        if self._workspace is None or self._workspace.numel() < need:
+            self._workspace = torch.empty(need, dtype=torch.uint8, device="cuda")
+        return self._workspace
+
+    def launch_attention(self, layer, q_rot, seq_lens, page_table, out=None):
+        """Decode attention (query_length == 1): one query token per stream."""
+        import torch
+
+        batch = q_rot.shape[0]
+        if out is None:
+            out = torch.empty_like(q_rot)
+        ws = self.workspace(batch)
+        _check(self.lib.qm_decode_attention(self.pool, layer, _ptr(q_rot), _ptr(seq_lens), _ptr(page_table),
+                                            page_table.shape[1], batch, self.q_heads, _ptr(out), _ptr(ws),
+                                            ws.numel(), _stream()))
+        return out
+
+    def launch_attention_partial(self, layer, q_rot, seq_lens, page_table, partial=None):
+        import torch
+
+        batch = q_rot.shape[0]
+        if partial is None:
+            partial = torch.empty((batch, self.q_heads, PARTIAL_STRIDE), dtype=torch.float32, device="cuda")
+        ws = self.workspace(batch)
+        _check(self.lib.qm_decode_attention_partial(self.pool, layer, _ptr(q_rot), _ptr(seq_lens), _ptr(page_table),
+                                                    page_table.shape[1], batch, self.q_heads, _ptr(partial),
+                                                    _ptr(ws), ws.numel(), _stream()))
+        return partial
+
+    def combine(self, partials, out=None):
+        """partials [parts][batch][q_heads][130] fp32 -> [batch][q_heads][128] bf16."""
+        import torch
+
+        parts, batch, heads = partials.shape[0], partials.shape[1], partials.shape[2]
+        if out is None:
+            out = torch.empty((batch, heads, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
+        _check(self.lib.qm_attention_combine(_ptr(partials), parts, batch * heads, _ptr(out), _stream()))
+        return out
+
+    def launch_attention_prefill(self, layer, q_rot, cu_seqlens, page_table, max_seqlen, start_positions=None,
+                                 out=None):
+        """Causal attention over packed varlen queries (query_length > 1)."""
+        import torch
+
+        total = q_rot.shape[0]
+        batch = cu_seqlens.shape[0] - 1
+        if out is None:
+            out = torch.empty_like(q_rot)
+        _check(self.lib.qm_prefill_attention_varlen(self.pool, layer, _ptr(q_rot), _ptr(cu_seqlens),
+                                                    _ptr(start_positions), _ptr(page_table), page_table.shape[1],
+                                                    batch, total, max_seqlen, self.q_heads, _ptr(out), _stream()))
+        return out
+
+
+def _wrap_device_pointer(ptr: int, shape, dtype):
+    """A torch tensor aliasing device memory owned by the library (valid while the pool lives)."""
+    import math
+
+    import torch
+
+    elems = math.prod(shape)
+
+    class _Holder:
+        pass
+
+    holder = _Holder()
+    holder.__cuda_array_interface__ = {
+        "shape": (elems,),
+        "typestr": "<i2",
+        "data": (int(ptr), False),
+        "version": 3,
+    }
+    flat = torch.as_tensor(holder, device="cuda")
+    return flat.view(dtype).view(shape)

@@ -1,0 +1,228 @@
+// Fused per-head RMSNorm + RoPE + paged KV append, for decode (one token per
+// stream) and packed varlen prefill.
+//
+// Stands in for talker_qk_norm_rope_cache_fused_kernel (17.cu:15412-15574) and
+// for the prefill sequence rmsnorm_kernel x2 (17.cu:8295-8357), talker_rope_rows_kernel
+// x2 (:15578-15673), talker_scatter_prefill_kv_kernel (:15677-15735).
+//
+// One warp owns one (token, head) row of 128 values: lane l holds dimensions
+// 4l..4l+3 (one 8-byte load/store per row, 256 B per warp).  The arithmetic
+// keeps the reference's five bf16 roundings per element and reproduces its
+// sum-of-squares reduction order, so the output bits equal the reference
+// kernel's: the reference reduces 128 per-thread squares with a shuffle-down
+// tree inside each 32-thread warp and then folds the four warp sums as
+// (w0 + w2) + (w1 + w3).  Here the 32 values of "warp" j sit in lanes 8j..8j+7,
+// and the same pairs are added in the same order with xor shuffles (float
+// addition commutes, so a + b from either side is the same value).
+#include "qm_common.cuh"
+
+namespace {
+
+constexpr int kAppendWarps = 8;
+
+struct AppendArgs {
+    const uint16_t* q;
+    const uint16_t* k;
+    const uint16_t* v;
+    const uint16_t* q_norm_weight;
+    const uint16_t* k_norm_weight;
+    const uint16_t* rope_cos;
+    const uint16_t* rope_sin;
+    const int32_t* positions;     // decode: [batch]; prefill: start_positions or null
+    const int32_t* cu_seqlens;    // null for decode
+    const int32_t* page_table;
+    uint16_t* q_rot;
+    uint16_t* key_pool;
+    uint16_t* value_pool;
+    uint32_t* status;
+    long long rows_total;         // tokens * (q_heads + kv_heads)
+    int rope_rows;
+    int max_pages;
+    int num_pages;
+    int batch;
+    int q_heads;
+    int kv_heads;
+    float epsilon;
+};
+
+__device__ __forceinline__ float reference_order_sum_of_squares(float s0, float s1, float s2, float s3) {
+    // Tree inside the 8-lane group holding one reference warp's 32 values.
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 4);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 4);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, 4);
+    s3 += __shfl_xor_sync(0xffffffffu, s3, 4);
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, 2);
+    s3 += __shfl_xor_sync(0xffffffffu, s3, 2);
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
+    s3 += __shfl_xor_sync(0xffffffffu, s3, 1);
+    s0 = __fadd_rn(s0, s2);
+    s1 = __fadd_rn(s1, s3);
+    const float warp_sum = __fadd_rn(s0, s1);      // exact in lanes 0, 8, 16, 24
+    const float w0 = __shfl_sync(0xffffffffu, warp_sum, 0);
+    const float w1 = __shfl_sync(0xffffffffu, warp_sum, 8);
+    const float w2 = __shfl_sync(0xffffffffu, warp_sum, 16);
+    const float w3 = __shfl_sync(0xffffffffu, warp_sum, 24);
+    return __fadd_rn(__fadd_rn(w0, w2), __fadd_rn(w1, w3));
+}
+
+__global__ void __launch_bounds__(kAppendWarps * 32) qm_norm_rope_append_kernel(const AppendArgs a) {
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * kAppendWarps + (threadIdx.x >> 5);
+    if (row >= a.rows_total) return;
+    const int heads = a.q_heads + a.kv_heads;
+    const int token = (int)(row / heads);
+    const int slot = (int)(row % heads);
+    const bool is_query = slot < a.q_heads;
+    const int head = is_query ? slot : slot - a.q_heads;
+
+    // Which stream and position this packed row belongs to.
+    int stream, position;
+    if (a.cu_seqlens == nullptr) {
+        stream = token;
+        position = a.positions[token];
+    } else {
+        if (token >= a.cu_seqlens[a.batch]) return;   // padding rows past the last sequence
+        int lo = 0, hi = a.batch;          // largest s with cu_seqlens[s] <= token
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (a.cu_seqlens[mid] <= token) lo = mid; else hi = mid;
+        }
+        stream = lo;
+        position = (a.positions ? a.positions[stream] : 0) + (token - a.cu_seqlens[stream]);
+    }
+    if (position < 0 || position >= a.rope_rows) {
+        if (lane == 0) atomicOr(a.status, QM_DEVSTAT_BAD_POS);
+        return;
+    }
+
+    const uint16_t* source = is_query ? a.q + ((size_t)token * a.q_heads + head) * kHeadDim
+                                      : a.k + ((size_t)token * a.kv_heads + head) * kHeadDim;
+    const uint2 raw = *reinterpret_cast<const uint2*>(source + 4 * lane);
+    const uint2 wraw = *reinterpret_cast<const uint2*>((is_query ? a.q_norm_weight : a.k_norm_weight) + 4 * lane);
+    const uint2 craw = *reinterpret_cast<const uint2*>(a.rope_cos + (size_t)position * kHeadDim + 4 * lane);
+    const uint2 sraw = *reinterpret_cast<const uint2*>(a.rope_sin + (size_t)position * kHeadDim + 4 * lane);
+
+    float x[4] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y)};
+    const float w[4] = {bf16_lo(wraw.x), bf16_hi(wraw.x), bf16_lo(wraw.y), bf16_hi(wraw.y)};
+    const float c[4] = {bf16_lo(craw.x), bf16_hi(craw.x), bf16_lo(craw.y), bf16_hi(craw.y)};
+    const float s[4] = {bf16_lo(sraw.x), bf16_hi(sraw.x), bf16_lo(sraw.y), bf16_hi(sraw.y)};
+
+    const float sum = reference_order_sum_of_squares(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]),
+                                                     __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
+    const float inverse_rms = rsqrtf(__fadd_rn(__fdiv_rn(sum, (float)kHeadDim), a.epsilon));
+
+    // RMSNorm: normalise in fp32 -> bf16 -> multiply by the bf16 weight -> bf16.
+    float n[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) n[i] = round_bf16(__fmul_rn(round_bf16(__fmul_rn(x[i], inverse_rms)), w[i]));
+
+    // rotate_half: dimension d pairs with d +- 64, which lane l ^ 16 holds.
+    uint32_t out_bits[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float partner = __shfl_xor_sync(0xffffffffu, n[i], 16);
+        if (lane < 16) partner = -partner;
+        const float first = round_bf16(__fmul_rn(n[i], c[i]));
+        const float second = round_bf16(__fmul_rn(partner, s[i]));
+        out_bits[i] = f32_to_bf16_bits(__fadd_rn(first, second));
+    }
+    const uint2 packed = make_uint2(out_bits[0] | (out_bits[1] << 16), out_bits[2] | (out_bits[3] << 16));
+
+    if (is_query) {
+        *reinterpret_cast<uint2*>(a.q_rot + ((size_t)token * a.q_heads + head) * kHeadDim + 4 * lane) = packed;
+        return;
+    }
+
+    if (position >= a.max_pages * kPageTokens) {
+        if (lane == 0) atomicOr(a.status, QM_DEVSTAT_BAD_POS);
+        return;
+    }
+    const int page = a.page_table[(size_t)stream * a.max_pages + (position >> 6)];
+    if (page < 0 || page >= a.num_pages) {
+        if (lane == 0) atomicOr(a.status, QM_DEVSTAT_BAD_PAGE);
+        return;
+    }
+    const size_t dst = (((size_t)page * a.kv_heads + head) * kPageTokens + (position & 63)) * kHeadDim + 4 * lane;
+    *reinterpret_cast<uint2*>(a.key_pool + dst) = packed;
+    *reinterpret_cast<uint2*>(a.value_pool + dst) =
+        *reinterpret_cast<const uint2*>(a.v + ((size_t)token * a.kv_heads + head) * kHeadDim + 4 * lane);
+}
+
+int32_t launch_append(qm_kv_pool* pool, int32_t layer, const AppendArgs& proto, long long tokens, cudaStream_t stream) {
+    AppendArgs a = proto;
+    a.key_pool = qm_kv_pool_key_ptr(pool, layer);
+    a.value_pool = qm_kv_pool_value_ptr(pool, layer);
+    a.status = pool->status_dev;
+    a.num_pages = pool->num_pages;
+    a.kv_heads = pool->kv_heads;
+    a.rows_total = tokens * (a.q_heads + a.kv_heads);
+    if (a.rows_total == 0) return QM_OK;
+    const long long blocks = (a.rows_total + kAppendWarps - 1) / kAppendWarps;
+    if (blocks > 0x7fffffffLL) return qm_fail(QM_ECAPACITY, "too many rows for one append launch");
+    qm_norm_rope_append_kernel<<<(unsigned)blocks, kAppendWarps * 32, 0, stream>>>(a);
+    QM_CUDA_TRY(cudaGetLastError(), "QK norm/RoPE/cache launch");
+    return QM_OK;
+}
+
+bool misaligned8(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) != 0; }
+
+}  // namespace
+
+extern "C" {
+
+int32_t qm_decode_append_rope(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const uint16_t* k,
+                              const uint16_t* v, const uint16_t* q_norm_weight, const uint16_t* k_norm_weight,
+                              const uint16_t* rope_cos, const uint16_t* rope_sin, int32_t rope_rows,
+                              const int32_t* positions, const int32_t* page_table, int32_t max_pages,
+                              int32_t batch, int32_t q_heads, float epsilon, uint16_t* q_rot, void* stream) {
+    if (!pool) return qm_fail(QM_EINVAL, "pool is null");
+    if (layer < 0 || layer >= pool->layers) return qm_fail(QM_EINVAL, "layer out of range");
+    if (!q || !k || !v || !q_norm_weight || !k_norm_weight || !rope_cos || !rope_sin || !positions || !page_table ||
+        !q_rot)
+        return qm_fail(QM_EINVAL, "null tensor pointer");
+    if (misaligned8(q) || misaligned8(k) || misaligned8(v) || misaligned8(q_norm_weight) || misaligned8(k_norm_weight) ||
+        misaligned8(rope_cos) || misaligned8(rope_sin) || misaligned8(q_rot))
+        return qm_fail(QM_EINVAL, "bf16 tensors must be 8-byte aligned");
+    if (batch < 0 || q_heads < 1 || max_pages < 1 || rope_rows < 1) return qm_fail(QM_EINVAL, "invalid geometry");
+    AppendArgs a{};
+    a.q = q; a.k = k; a.v = v;
+    a.q_norm_weight = q_norm_weight; a.k_norm_weight = k_norm_weight;
+    a.rope_cos = rope_cos; a.rope_sin = rope_sin;
+    a.positions = positions; a.cu_seqlens = nullptr; a.page_table = page_table;
+    a.q_rot = q_rot;
+    a.rope_rows = rope_rows; a.max_pages = max_pages; a.batch = batch; a.q_heads = q_heads; a.epsilon = epsilon;
+    return launch_append(pool, layer, a, batch, static_cast<cudaStream_t>(stream));
+}
+
+int32_t qm_prefill_append_rope_varlen(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const uint16_t* k,
+                                      const uint16_t* v, const uint16_t* q_norm_weight,
+                                      const uint16_t* k_norm_weight, const uint16_t* rope_cos,
+                                      const uint16_t* rope_sin, int32_t rope_rows, const int32_t* cu_seqlens,
+                                      const int32_t* start_positions, const int32_t* page_table,
+                                      int32_t max_pages, int32_t batch, int32_t total_tokens, int32_t q_heads,
+                                      float epsilon, uint16_t* q_rot, void* stream) {
+    if (!pool) return qm_fail(QM_EINVAL, "pool is null");
+    if (layer < 0 || layer >= pool->layers) return qm_fail(QM_EINVAL, "layer out of range");
+    if (!q || !k || !v || !q_norm_weight || !k_norm_weight || !rope_cos || !rope_sin || !cu_seqlens || !page_table ||
+        !q_rot)
+        return qm_fail(QM_EINVAL, "null tensor pointer");
+    if (misaligned8(q) || misaligned8(k) || misaligned8(v) || misaligned8(q_norm_weight) || misaligned8(k_norm_weight) ||
+        misaligned8(rope_cos) || misaligned8(rope_sin) || misaligned8(q_rot))
+        return qm_fail(QM_EINVAL, "bf16 tensors must be 8-byte aligned");
+    if (batch < 1 || total_tokens < 0 || q_heads < 1 || max_pages < 1 || rope_rows < 1)
+        return qm_fail(QM_EINVAL, "invalid geometry");
+    AppendArgs a{};
+    a.q = q; a.k = k; a.v = v;
+    a.q_norm_weight = q_norm_weight; a.k_norm_weight = k_norm_weight;
+    a.rope_cos = rope_cos; a.rope_sin = rope_sin;
+    a.positions = start_positions; a.cu_seqlens = cu_seqlens; a.page_table = page_table;
+    a.q_rot = q_rot;
+    a.rope_rows = rope_rows; a.max_pages = max_pages; a.batch = batch; a.q_heads = q_heads; a.epsilon = epsilon;
+    return launch_append(pool, layer, a, total_tokens, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

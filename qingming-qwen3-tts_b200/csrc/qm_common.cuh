@@ -1,0 +1,130 @@
+// Shared declarations of the talker attention library: the pool object, error
+// reporting, bf16 helpers and the sm_100a PTX wrappers (mbarrier, bulk copies)
+// the kernels use.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda.h>
+#include <stdint.h>
+
+#include "../../include/qm_attention.h"
+
+constexpr int kHeadDim = QM_HEAD_DIM;        // 128
+constexpr int kPageTokens = QM_PAGE_TOKENS;  // 64
+constexpr int kTileElems = kPageTokens * kHeadDim;   // one (page, kv head) tile
+constexpr int kTileBytes = kTileElems * 2;           // 16 KB
+
+struct qm_kv_pool {
+    int device;
+    int layers;
+    int num_pages;
+    int kv_heads;
+    int sm_count;
+    size_t layer_elems;      // num_pages * kv_heads * 64 * 128
+    uint16_t* key;           // [layers][num_pages][kv_heads][64][128]
+    uint16_t* value;
+    uint32_t* status_dev;    // QM_DEVSTAT_* bits, written by kernels
+    // Tiled tensor maps over one layer's pool viewed as rows of 128 bf16
+    // (rows = num_pages * kv_heads * 64), built at creation for the prefill kernel.
+    CUtensorMap* key_maps;   // host array [layers]
+    CUtensorMap* value_maps;
+};
+
+// Records `text` as this thread's last error and returns `code`.
+int32_t qm_fail(int32_t code, const char* text);
+int32_t qm_fail_cuda(cudaError_t status, const char* operation);
+
+#define QM_CUDA_TRY(expr, what)                                        \
+    do {                                                               \
+        cudaError_t qm_cuda_status = (expr);                           \
+        if (qm_cuda_status != cudaSuccess) return qm_fail_cuda(qm_cuda_status, what); \
+    } while (0)
+
+#ifdef __CUDACC__
+
+// ---- bf16 <-> f32, bit-level (same rounding as 17.cu:15082-15104)
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t v) { return __uint_as_float(v << 16); }
+
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float value) {
+    uint32_t bits = __float_as_uint(value);
+    if ((bits & 0x7fffffffu) > 0x7f800000u) return (bits >> 16) | 0x0040u;
+    bits += 0x7fffu + ((bits >> 16) & 1u);
+    return bits >> 16;
+}
+
+__device__ __forceinline__ float round_bf16(float v) { return bf16_bits_to_f32(f32_to_bf16_bits(v)); }
+
+// Low / high bf16 of a packed pair, widened.
+__device__ __forceinline__ float bf16_lo(uint32_t pair) { return __uint_as_float(pair << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t pair) { return __uint_as_float(pair & 0xffff0000u); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ---- mbarrier / bulk-copy wrappers (shared::cta addresses as 32-bit)
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait.  Returns false when the limit ran out; the caller records
+// QM_DEVSTAT_TIMEOUT and carries on with uniform control flow (the data is then
+// garbage and the host sees the status bit), so no thread is left behind at a
+// later barrier.  `dead` short-circuits every wait after the first failure.
+constexpr uint32_t kWaitSpinLimit = 1u << 21;
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, bool& dead) {
+    if (dead) return false;
+    for (uint32_t spin = 0; spin < kWaitSpinLimit; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (spin > 256) __nanosleep(128);
+    }
+    dead = true;
+    return false;
+}
+
+// 1-D bulk copy global -> shared::cta, completion counted on an mbarrier.
+// Both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+#endif  // __CUDACC__

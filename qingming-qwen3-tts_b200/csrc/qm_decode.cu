@@ -1,0 +1,547 @@
+// Split-KV flash decoding over the paged bf16 KV cache (GQA group of 2), plus
+// the log-sum-exp combine kernels.
+//
+// Stands in for talker_attention_gqa2_m1_locality_kernel (17.cu:16061-16251,
+// dispatch :17916-17952): one new query token per stream, both query heads that
+// share a KV head are served by the same K/V read.  Where the reference runs 8
+// CTAs and materialises bf16 scores in shared memory, this kernel
+//
+//   * flattens the work into units, one unit = one (stream, kv head, page)
+//     tile pair (K tile + V tile, 16 KB each, contiguous in the pool), ordered
+//     stream-major, then kv head, then page;
+//   * gives each of G = 2 x SM-count CTAs an equal contiguous run of units
+//     (ragged lengths balance to within one tile);
+//   * streams the tiles through a 3-stage shared-memory ring with 1-D bulk
+//     copies (cp.async.bulk + mbarrier complete_tx) issued by a producer warp,
+//     while 8 consumer warps keep an fp32 online softmax per run of units that
+//     belong to the same (stream, kv head) segment;
+//   * writes a segment's result directly when one CTA saw all of it, else an
+//     (m, l, o) partial into slot (cta + segment) of the workspace - that map
+//     is injective over the (cta, segment) pairs that occur because both
+//     indices only grow along the unit order - and a second kernel folds the
+//     partials in CTA order, so results do not depend on timing.
+//
+// Scores live in the log2 domain (q is pre-multiplied by scale * log2 e).
+#include <math_constants.h>
+
+#include "qm_common.cuh"
+
+namespace {
+
+constexpr int kStages = 3;
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kDecodeThreads = kConsumerThreads + 32;
+constexpr int kStageBytes = 2 * kTileBytes;
+constexpr int kMaxBatchPerLaunch = 512;
+constexpr int kMaxGrid = 1024;
+constexpr int kPartialStride = kHeadDim + 2;   // m, l, o[128]
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct DecodeArgs {
+    const uint16_t* q_rot;
+    const uint16_t* key_pool;
+    const uint16_t* value_pool;
+    const int32_t* seq_lens;
+    const int32_t* page_table;
+    uint16_t* out;           // mode 0
+    float* partial_out;      // mode 1: [batch][q_heads][130]
+    float* ws_partials;      // [(grid + segments)][2][130]
+    int32_t* ws_first;       // [segments] first CTA that holds part of the segment
+    int32_t* ws_last;        // [segments] last CTA
+    uint32_t* status;
+    int batch;
+    int kv_heads;
+    int max_pages;
+    int num_pages;
+    int mode;
+};
+
+struct SharedLayout {
+    static constexpr int kStagesOff = 0;
+    static constexpr int kPrefixOff = kStages * kStageBytes;                       // int32[kMaxBatch+1]
+    static constexpr int kScoreOff = kPrefixOff + ((kMaxBatchPerLaunch + 1) * 4 + 15) / 16 * 16;
+    static constexpr int kMergeOff = kScoreOff + 2 * 2 * kPageTokens * 4;          // float[2][2][64]
+    static constexpr int kMergeLOff = kMergeOff + kConsumerWarps * 2 * kHeadDim * 4;
+    static constexpr int kMetaOff = kMergeLOff + kConsumerWarps * 2 * 4;
+    static constexpr int kBarOff = kMetaOff + kStages * 16;
+    static constexpr int kTotal = kBarOff + 2 * kStages * 8;
+};
+
+__device__ __forceinline__ int clamp_len(int len, int max_pages, uint32_t* status) {
+    if (len < 0) len = 0;
+    const int cap = max_pages * kPageTokens;
+    if (len > cap) {
+        atomicOr(status, QM_DEVSTAT_BAD_POS);
+        len = cap;
+    }
+    return len;
+}
+
+__global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(const DecodeArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    int32_t* prefix = reinterpret_cast<int32_t*>(smem + SharedLayout::kPrefixOff);
+    float* score = reinterpret_cast<float*>(smem + SharedLayout::kScoreOff);
+    float* merge_o = reinterpret_cast<float*>(smem + SharedLayout::kMergeOff);
+    float* merge_l = reinterpret_cast<float*>(smem + SharedLayout::kMergeLOff);
+    int4* meta = reinterpret_cast<int4*>(smem + SharedLayout::kMetaOff);
+    const uint32_t bar_base = smem_addr(smem + SharedLayout::kBarOff);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int hkv = a.kv_heads;
+
+    // Units per stream, then an inclusive scan -> prefix[s] = first unit of stream s.
+    for (int s = tid; s < a.batch; s += kDecodeThreads) {
+        const int len = clamp_len(a.seq_lens[s], a.max_pages, a.status);
+        prefix[s + 1] = ((len + kPageTokens - 1) >> 6) * hkv;
+    }
+    if (tid == 0) {
+        prefix[0] = 0;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), kConsumerWarps);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int carry = 0;
+        for (int base = 0; base < a.batch; base += 32) {
+            const int idx = base + lane;
+            int v = idx < a.batch ? prefix[idx + 1] : 0;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, v, off);
+                if (lane >= off) v += t;
+            }
+            v += carry;
+            if (idx < a.batch) prefix[idx + 1] = v;
+            carry = __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+
+    const long long total_units = prefix[a.batch];
+    const long long grid_eff = total_units < (long long)gridDim.x ? total_units : (long long)gridDim.x;
+    const int cta = blockIdx.x;
+    if (cta >= grid_eff) return;
+    const long long unit_begin = (long long)cta * total_units / grid_eff;
+    const long long unit_end = (long long)(cta + 1) * total_units / grid_eff;
+    const int count = (int)(unit_end - unit_begin);
+
+    bool dead = false;
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------ producer
+        for (int base = 0; base < count; base += 32) {
+            int seg_l = 0, page_idx_l = 0, pages_l = 1, page_id_l = 0, nvalid_l = 0, head_l = 0;
+            if (base + lane < count) {
+                const int u = (int)(unit_begin + base + lane);
+                int lo = 0, hi = a.batch;       // largest s with prefix[s] <= u and units in s
+                while (hi - lo > 1) {
+                    const int mid = (lo + hi) >> 1;
+                    if (prefix[mid] <= u) lo = mid; else hi = mid;
+                }
+                const int s = lo;
+                const int r = u - prefix[s];
+                pages_l = (prefix[s + 1] - prefix[s]) / hkv;
+                head_l = r / pages_l;
+                page_idx_l = r - head_l * pages_l;
+                seg_l = s * hkv + head_l;
+                const int len = clamp_len(a.seq_lens[s], a.max_pages, a.status);
+                const int left = len - page_idx_l * kPageTokens;
+                nvalid_l = left < kPageTokens ? left : kPageTokens;
+                page_id_l = a.page_table[(size_t)s * a.max_pages + page_idx_l];
+                if (page_id_l < 0 || page_id_l >= a.num_pages) {
+                    atomicOr(a.status, QM_DEVSTAT_BAD_PAGE);
+                    page_id_l = 0;
+                }
+            }
+            const int batch_units = count - base < 32 ? count - base : 32;
+            for (int j = 0; j < batch_units; ++j) {
+                const int seg = __shfl_sync(0xffffffffu, seg_l, j);
+                const int page_idx = __shfl_sync(0xffffffffu, page_idx_l, j);
+                const int pages = __shfl_sync(0xffffffffu, pages_l, j);
+                const int page_id = __shfl_sync(0xffffffffu, page_id_l, j);
+                const int nvalid = __shfl_sync(0xffffffffu, nvalid_l, j);
+                const int head = __shfl_sync(0xffffffffu, head_l, j);
+                if (lane == 0) {
+                    const int n = base + j;
+                    const int stage = n % kStages;
+                    const uint32_t parity = ((n / kStages) & 1) ^ 1;
+                    if (!mbar_wait_bounded(empty_bar(stage), parity, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                    meta[stage] = make_int4(seg, page_idx, pages, nvalid);
+                    const uint32_t bytes = (uint32_t)nvalid * kHeadDim * 2;
+                    const size_t tile = ((size_t)page_id * hkv + head) * kTileElems;
+                    const uint32_t dst = smem_addr(smem + stage * kStageBytes);
+                    mbar_arrive_expect_tx(full_bar(stage), 2 * bytes);
+                    bulk_copy_g2s(dst, a.key_pool + tile, bytes, full_bar(stage));
+                    bulk_copy_g2s(dst + kTileBytes, a.value_pool + tile, bytes, full_bar(stage));
+                }
+                __syncwarp();
+            }
+        }
+        // The consumers wait for every tile before they finish, so no copy is in
+        // flight when the CTA retires unless a wait gave up; in that case wait
+        // (bounded again) for the last copies issued.
+        if (lane == 0 && dead) {
+            bool ignore = false;
+            const int first = count > kStages ? count - kStages : 0;
+            for (int n = first; n < count; ++n) mbar_wait_bounded(full_bar(n % kStages), (n / kStages) & 1, ignore);
+        }
+        return;
+    }
+
+    // --------------------------------------------------------------- consumers
+    const int half = lane >> 4;
+    const int lp = lane & 15;
+    float q0[8], q1[8], o0[8], o1[8];
+    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.0f, l1 = 0.0f;
+    bool seg_from_start = false;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q0[j] = q1[j] = o0[j] = o1[j] = 0.0f;
+
+    for (int n = 0; n < count; ++n) {
+        const int stage = n % kStages;
+        if (!mbar_wait_bounded(full_bar(stage), (n / kStages) & 1, dead) && lane == 0)
+            atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+        const int4 mt = meta[stage];
+        const int seg = mt.x, page_idx = mt.y, pages = mt.z, nvalid = mt.w;
+        const int stream = seg / hkv;
+        const int head = seg - stream * hkv;
+
+        if (n == 0 || page_idx == 0) {
+            // New segment: fetch the two query heads of this KV head.
+            const float qscale = kLog2e / sqrtf((float)kHeadDim);
+            const uint16_t* qp = a.q_rot + ((size_t)stream * (2 * hkv) + 2 * head) * kHeadDim + 8 * lp;
+            const uint4 qa = *reinterpret_cast<const uint4*>(qp);
+            const uint4 qb = *reinterpret_cast<const uint4*>(qp + kHeadDim);
+            q0[0] = bf16_lo(qa.x) * qscale; q0[1] = bf16_hi(qa.x) * qscale;
+            q0[2] = bf16_lo(qa.y) * qscale; q0[3] = bf16_hi(qa.y) * qscale;
+            q0[4] = bf16_lo(qa.z) * qscale; q0[5] = bf16_hi(qa.z) * qscale;
+            q0[6] = bf16_lo(qa.w) * qscale; q0[7] = bf16_hi(qa.w) * qscale;
+            q1[0] = bf16_lo(qb.x) * qscale; q1[1] = bf16_hi(qb.x) * qscale;
+            q1[2] = bf16_lo(qb.y) * qscale; q1[3] = bf16_hi(qb.y) * qscale;
+            q1[4] = bf16_lo(qb.z) * qscale; q1[5] = bf16_hi(qb.z) * qscale;
+            q1[6] = bf16_lo(qb.w) * qscale; q1[7] = bf16_hi(qb.w) * qscale;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o0[j] = o1[j] = 0.0f;
+            m0 = m1 = -CUDART_INF_F;
+            l0 = l1 = 0.0f;
+            seg_from_start = page_idx == 0;
+        }
+
+        const unsigned char* ktile = smem + stage * kStageBytes;
+        const unsigned char* vtile = ktile + kTileBytes;
+        float* sc = score + (n & 1) * (2 * kPageTokens);
+
+        // ---- scores: 8 keys per warp, half-warp per key row
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int key = 8 * warp + 2 * i + half;
+            const uint4 kk = *reinterpret_cast<const uint4*>(ktile + key * (kHeadDim * 2) + lp * 16);
+            const float kf[8] = {bf16_lo(kk.x), bf16_hi(kk.x), bf16_lo(kk.y), bf16_hi(kk.y),
+                                 bf16_lo(kk.z), bf16_hi(kk.z), bf16_lo(kk.w), bf16_hi(kk.w)};
+            float d0 = 0.0f, d1 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                d0 = fmaf(q0[j], kf[j], d0);
+                d1 = fmaf(q1[j], kf[j], d1);
+            }
+            acc[2 * i] = d0;
+            acc[2 * i + 1] = d1;
+        }
+        {
+            // Reduce-scatter over the 16 lanes of a half-warp: 8 values -> lane
+            // lp ends with value index lp >> 1 (duplicated in the odd lane).
+            float r[4], r2[2];
+            const bool b3 = (lp & 8) != 0, b2 = (lp & 4) != 0, b1 = (lp & 2) != 0;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float mine = b3 ? acc[4 + t] : acc[t];
+                const float theirs = b3 ? acc[t] : acc[4 + t];
+                r[t] = mine + __shfl_xor_sync(0xffffffffu, theirs, 8);
+            }
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const float mine = b2 ? r[2 + t] : r[t];
+                const float theirs = b2 ? r[t] : r[2 + t];
+                r2[t] = mine + __shfl_xor_sync(0xffffffffu, theirs, 4);
+            }
+            const float mine = b1 ? r2[1] : r2[0];
+            const float theirs = b1 ? r2[0] : r2[1];
+            float r3 = mine + __shfl_xor_sync(0xffffffffu, theirs, 2);
+            r3 += __shfl_xor_sync(0xffffffffu, r3, 1);
+            const int idx = lp >> 1;
+            const int key = 8 * warp + 2 * (idx >> 1) + half;
+            if ((lp & 1) == 0) sc[(idx & 1) * kPageTokens + key] = key < nvalid ? r3 : -CUDART_INF_F;
+        }
+        named_bar_sync(1, kConsumerThreads);
+
+        // ---- online softmax over the 64 keys of the tile (same in every warp)
+        float x0 = fmaxf(sc[lane], sc[lane + 32]);
+        float x1 = fmaxf(sc[kPageTokens + lane], sc[kPageTokens + lane + 32]);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, off));
+            x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, off));
+        }
+        const float mn0 = fmaxf(m0, x0), mn1 = fmaxf(m1, x1);
+        if (mn0 != m0 || mn1 != m1) {
+            const float c0 = fast_exp2(m0 - mn0), c1 = fast_exp2(m1 - mn1);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                o0[j] *= c0;
+                o1[j] *= c1;
+            }
+            l0 *= c0;
+            l1 *= c1;
+            m0 = mn0;
+            m1 = mn1;
+        }
+
+        // ---- P V for this warp's 8 keys
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int key = 8 * warp + 2 * i + half;
+            if (key < nvalid) {
+                const float p0 = fast_exp2(sc[key] - m0);
+                const float p1 = fast_exp2(sc[kPageTokens + key] - m1);
+                l0 += p0;
+                l1 += p1;
+                const uint4 vv = *reinterpret_cast<const uint4*>(vtile + key * (kHeadDim * 2) + lp * 16);
+                const float vf[8] = {bf16_lo(vv.x), bf16_hi(vv.x), bf16_lo(vv.y), bf16_hi(vv.y),
+                                     bf16_lo(vv.z), bf16_hi(vv.z), bf16_lo(vv.w), bf16_hi(vv.w)};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    o0[j] = fmaf(p0, vf[j], o0[j]);
+                    o1[j] = fmaf(p1, vf[j], o1[j]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(stage));
+
+        // ---- end of this CTA's share of the segment
+        if (n == count - 1 || page_idx == pages - 1) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                o0[j] += __shfl_xor_sync(0xffffffffu, o0[j], 16);
+                o1[j] += __shfl_xor_sync(0xffffffffu, o1[j], 16);
+            }
+            l0 += __shfl_xor_sync(0xffffffffu, l0, 16);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, 16);
+            if (half == 0) {
+                float* dst0 = merge_o + (warp * 2 + 0) * kHeadDim + 8 * lp;
+                float* dst1 = merge_o + (warp * 2 + 1) * kHeadDim + 8 * lp;
+                *reinterpret_cast<float4*>(dst0) = make_float4(o0[0], o0[1], o0[2], o0[3]);
+                *reinterpret_cast<float4*>(dst0 + 4) = make_float4(o0[4], o0[5], o0[6], o0[7]);
+                *reinterpret_cast<float4*>(dst1) = make_float4(o1[0], o1[1], o1[2], o1[3]);
+                *reinterpret_cast<float4*>(dst1 + 4) = make_float4(o1[4], o1[5], o1[6], o1[7]);
+            }
+            if (lane == 0) {
+                merge_l[warp * 2 + 0] = l0;
+                merge_l[warp * 2 + 1] = l1;
+            }
+            named_bar_sync(1, kConsumerThreads);
+            {
+                const int qh = tid >> 7;           // which of the two query heads
+                const int d = tid & 127;
+                float sum = 0.0f, lsum = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) {
+                    sum += merge_o[(w * 2 + qh) * kHeadDim + d];
+                    lsum += merge_l[w * 2 + qh];
+                }
+                const float m = qh ? m1 : m0;
+                const bool whole = seg_from_start && page_idx == pages - 1;
+                const size_t row = (size_t)stream * (2 * hkv) + 2 * head + qh;
+                if (whole && a.mode == 0) {
+                    a.out[row * kHeadDim + d] = (uint16_t)f32_to_bf16_bits(sum / lsum);
+                } else {
+                    float* dst = whole ? a.partial_out + row * kPartialStride
+                                       : a.ws_partials + ((size_t)(cta + seg) * 2 + qh) * kPartialStride;
+                    dst[2 + d] = sum;
+                    if (d == 0) {
+                        dst[0] = whole ? m * kLn2 : m;
+                        dst[1] = lsum;
+                    }
+                }
+                if (tid == 0) {
+                    if (seg_from_start) a.ws_first[seg] = cta;
+                    if (page_idx == pages - 1) a.ws_last[seg] = cta;
+                }
+            }
+            named_bar_sync(1, kConsumerThreads);
+        }
+    }
+}
+
+// Folds the per-CTA partials of one (stream, kv head) segment, in CTA order.
+__global__ void __launch_bounds__(256) qm_decode_combine_kernel(const DecodeArgs a, int grid_main) {
+    const int seg = blockIdx.x;
+    const int hkv = a.kv_heads;
+    const int stream = seg / hkv;
+    const int head = seg - stream * hkv;
+    const int qh = threadIdx.x >> 7;
+    const int d = threadIdx.x & 127;
+    const size_t row = (size_t)stream * (2 * hkv) + 2 * head + qh;
+    const int len = a.seq_lens[stream];
+    if (len <= 0) {
+        if (a.mode == 0) {
+            a.out[row * kHeadDim + d] = 0;
+        } else {
+            float* dst = a.partial_out + row * kPartialStride;
+            dst[2 + d] = 0.0f;
+            if (d == 0) {
+                dst[0] = -CUDART_INF_F;
+                dst[1] = 0.0f;
+            }
+        }
+        return;
+    }
+    const int first = a.ws_first[seg], last = a.ws_last[seg];
+    if (first == last) return;       // the main kernel wrote this segment itself
+    if (first < 0 || last >= grid_main || last < first) {
+        if (threadIdx.x == 0) atomicOr(a.status, QM_DEVSTAT_BAD_PAGE);
+        return;
+    }
+    float big = -CUDART_INF_F;
+    for (int c = first; c <= last; ++c)
+        big = fmaxf(big, a.ws_partials[((size_t)(c + seg) * 2 + qh) * kPartialStride]);
+    float acc = 0.0f, denom = 0.0f;
+    for (int c = first; c <= last; ++c) {
+        const float* src = a.ws_partials + ((size_t)(c + seg) * 2 + qh) * kPartialStride;
+        const float w = fast_exp2(src[0] - big);
+        denom = fmaf(w, src[1], denom);
+        acc = fmaf(w, src[2 + d], acc);
+    }
+    if (a.mode == 0) {
+        a.out[row * kHeadDim + d] = (uint16_t)f32_to_bf16_bits(acc / denom);
+    } else {
+        float* dst = a.partial_out + row * kPartialStride;
+        dst[2 + d] = acc;
+        if (d == 0) {
+            dst[0] = big * kLn2;
+            dst[1] = denom;
+        }
+    }
+}
+
+// partials [parts][rows][130] (m in natural-log domain) -> out [rows][128] bf16.
+__global__ void __launch_bounds__(128) qm_combine_partials_kernel(const float* __restrict__ partials, int parts,
+                                                                  int rows, uint16_t* __restrict__ out) {
+    const int row = blockIdx.x;
+    const int d = threadIdx.x;
+    float big = -CUDART_INF_F;
+    for (int g = 0; g < parts; ++g) big = fmaxf(big, partials[((size_t)g * rows + row) * kPartialStride]);
+    float acc = 0.0f, denom = 0.0f;
+    for (int g = 0; g < parts; ++g) {
+        const float* src = partials + ((size_t)g * rows + row) * kPartialStride;
+        if (!(src[1] > 0.0f)) continue;
+        const float w = __expf(src[0] - big);
+        denom = fmaf(w, src[1], denom);
+        acc = fmaf(w, src[2 + d], acc);
+    }
+    out[(size_t)row * kHeadDim + d] = denom > 0.0f ? (uint16_t)f32_to_bf16_bits(acc / denom) : (uint16_t)0;
+}
+
+size_t partials_bytes(int segments) { return (size_t)(kMaxGrid + segments) * 2 * kPartialStride * sizeof(float); }
+
+int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const int32_t* seq_lens,
+                   const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads, uint16_t* out,
+                   float* partial_out, void* workspace, int64_t workspace_bytes, cudaStream_t stream, int mode) {
+    if (!pool) return qm_fail(QM_EINVAL, "pool is null");
+    if (layer < 0 || layer >= pool->layers) return qm_fail(QM_EINVAL, "layer out of range");
+    if (!q_rot || !seq_lens || !page_table || !workspace || (mode == 0 ? !out : !partial_out))
+        return qm_fail(QM_EINVAL, "null tensor pointer");
+    if (q_heads != 2 * pool->kv_heads)
+        return qm_fail(QM_EINVAL, "decode attention needs q_heads == 2 * kv_heads (GQA group of 2)");
+    if (batch < 0 || max_pages < 1) return qm_fail(QM_EINVAL, "invalid geometry");
+    if ((reinterpret_cast<uintptr_t>(q_rot) & 15u) || (reinterpret_cast<uintptr_t>(workspace) & 15u))
+        return qm_fail(QM_EINVAL, "q_rot and workspace must be 16-byte aligned");
+    if (workspace_bytes < qm_decode_workspace_bytes(batch, pool->kv_heads))
+        return qm_fail(QM_EINVAL, "workspace smaller than qm_decode_workspace_bytes()");
+    if (batch == 0) return QM_OK;
+
+    static thread_local int attr_device = -1;
+    if (attr_device != pool->device) {
+        QM_CUDA_TRY(cudaFuncSetAttribute(qm_decode_splitkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SharedLayout::kTotal),
+                    "raise decode kernel shared memory");
+        attr_device = pool->device;
+    }
+    int grid = 2 * pool->sm_count;
+    if (grid > kMaxGrid) grid = kMaxGrid;
+
+    const int chunk_cap = kMaxBatchPerLaunch;
+    const int segs_cap = (batch < chunk_cap ? batch : chunk_cap) * pool->kv_heads;
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    DecodeArgs a{};
+    a.key_pool = qm_kv_pool_key_ptr(pool, layer);
+    a.value_pool = qm_kv_pool_value_ptr(pool, layer);
+    a.ws_partials = reinterpret_cast<float*>(ws);
+    a.ws_first = reinterpret_cast<int32_t*>(ws + partials_bytes(segs_cap));
+    a.ws_last = a.ws_first + segs_cap;
+    a.status = pool->status_dev;
+    a.kv_heads = pool->kv_heads;
+    a.max_pages = max_pages;
+    a.num_pages = pool->num_pages;
+    a.mode = mode;
+    for (int begin = 0; begin < batch; begin += chunk_cap) {
+        const int n = batch - begin < chunk_cap ? batch - begin : chunk_cap;
+        a.q_rot = q_rot + (size_t)begin * q_heads * kHeadDim;
+        a.seq_lens = seq_lens + begin;
+        a.page_table = page_table + (size_t)begin * max_pages;
+        a.out = out ? out + (size_t)begin * q_heads * kHeadDim : nullptr;
+        a.partial_out = partial_out ? partial_out + (size_t)begin * q_heads * kPartialStride : nullptr;
+        a.batch = n;
+        qm_decode_splitkv_kernel<<<grid, kDecodeThreads, SharedLayout::kTotal, stream>>>(a);
+        QM_CUDA_TRY(cudaGetLastError(), "split-KV decode attention launch");
+        qm_decode_combine_kernel<<<n * pool->kv_heads, 256, 0, stream>>>(a, grid);
+        QM_CUDA_TRY(cudaGetLastError(), "decode attention combine launch");
+    }
+    return QM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t qm_decode_workspace_bytes(int32_t batch, int32_t kv_heads) {
+    if (batch < 0 || kv_heads < 1) return 0;
+    const int segs = (batch < kMaxBatchPerLaunch ? batch : kMaxBatchPerLaunch) * kv_heads;
+    return (int64_t)partials_bytes(segs) + (int64_t)segs * 2 * sizeof(int32_t) + 256;
+}
+
+int32_t qm_decode_attention(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const int32_t* seq_lens,
+                            const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads,
+                            uint16_t* out, void* workspace, int64_t workspace_bytes, void* stream) {
+    return run_decode(pool, layer, q_rot, seq_lens, page_table, max_pages, batch, q_heads, out, nullptr, workspace,
+                      workspace_bytes, static_cast<cudaStream_t>(stream), 0);
+}
+
+int32_t qm_decode_attention_partial(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot,
+                                    const int32_t* seq_lens, const int32_t* page_table, int32_t max_pages,
+                                    int32_t batch, int32_t q_heads, float* partial, void* workspace,
+                                    int64_t workspace_bytes, void* stream) {
+    return run_decode(pool, layer, q_rot, seq_lens, page_table, max_pages, batch, q_heads, nullptr, partial,
+                      workspace, workspace_bytes, static_cast<cudaStream_t>(stream), 1);
+}
+
+int32_t qm_attention_combine(const float* partials, int32_t parts, int32_t rows, uint16_t* out, void* stream) {
+    if (!partials || !out) return qm_fail(QM_EINVAL, "null tensor pointer");
+    if (parts < 1 || rows < 0) return qm_fail(QM_EINVAL, "parts must be >= 1 and rows >= 0");
+    if (rows == 0) return QM_OK;
+    qm_combine_partials_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(partials, parts, rows, out);
+    QM_CUDA_TRY(cudaGetLastError(), "attention combine launch");
+    return QM_OK;
+}
+
+}  // extern "C"
