@@ -142,6 +142,29 @@ int32_t qm_decode_attention(qm_kv_pool* pool, int32_t layer, const uint16_t* q_r
                             const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads,
                             uint16_t* out, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Decode attention without any allocation, here or in the caller.  No counterpart
+ * in the reference, whose engine allocates all workspace at construction.
+ * Same inputs, outputs and result as qm_decode_attention, but the scratch
+ * lives in a fixed array inside the library (about 1.6 MB of device memory on
+ * every GPU that loads the library, held until the process exits).  Meant for
+ * hosts that cannot cudaMalloc on this path: a resident serving loop whose
+ * device memory was budgeted at start-up and whose second stream (the codec
+ * decoder) would be stalled by the device-wide synchronisation an allocation
+ * implies, or an engine whose own allocator already holds all device memory.
+ *   - at most 64 streams and 8 KV heads per call; more returns QM_ECAPACITY.
+ *   - the first call on each device looks up the array's device address (the
+ *     pool's device must be current); make that first call before starting
+ *     any stream capture.
+ *   - all calls on a device share the one array and it keeps what the last
+ *     call wrote; nothing in it needs clearing between calls, but two calls
+ *     whose kernels overlap on the GPU (different streams, or several
+ *     threads) would overwrite each other's partials: issue them on one
+ *     stream, or order them with events.
+ * Calls no cudaMalloc / cudaFree and no allocating library routine. */
+int32_t qm_decode_attention_static(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot,
+                                   const int32_t* seq_lens, const int32_t* page_table, int32_t max_pages,
+                                   int32_t batch, int32_t q_heads, uint16_t* out, void* stream);
+
 /* Same, but stops before normalisation and returns the partial softmax state
  * of each (stream, query head) over the keys held in THIS pool:
  *   partial [batch][q_heads][130] fp32 = { m (max scaled score, natural-log

@@ -62,6 +62,8 @@ ABI = {
     "qm_decode_workspace_bytes": (c_int64, [c_int32, c_int32]),
     "qm_decode_attention": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                       c_void_p, c_void_p, c_int64, c_void_p]),
+    "qm_decode_attention_static": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
+                                             c_int32, c_void_p, c_void_p]),
     "qm_decode_attention_partial": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
                                               c_int32, c_void_p, c_void_p, c_int64, c_void_p]),
     "qm_attention_combine": (c_int32, [c_void_p, c_int32, c_int32, c_void_p, c_void_p]),
@@ -220,6 +222,17 @@ class TalkerAttention:
         _check(self.lib.qm_decode_attention(self.pool, layer, _ptr(q_rot), _ptr(seq_lens), _ptr(page_table),
                                             page_table.shape[1], batch, self.q_heads, _ptr(out), _ptr(ws),
                                             ws.numel(), _stream()))
+        return out
+
+    def launch_attention_static(self, layer, q_rot, seq_lens, page_table, out=None):
+        """Decode attention through the entry point that uses the library's built-in scratch (no workspace)."""
+        import torch
+
+        batch = q_rot.shape[0]
+        if out is None:
+            out = torch.empty_like(q_rot)
+        _check(self.lib.qm_decode_attention_static(self.pool, layer, _ptr(q_rot), _ptr(seq_lens), _ptr(page_table),
+                                                   page_table.shape[1], batch, self.q_heads, _ptr(out), _stream()))
         return out
 
     def launch_attention_partial(self, layer, q_rot, seq_lens, page_table, partial=None):

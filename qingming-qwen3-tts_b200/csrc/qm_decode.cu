@@ -24,6 +24,8 @@
 // Scores live in the log2 domain (q is pre-multiplied by scale * log2 e).
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "qm_common.cuh"
 
 namespace {
@@ -545,3 +547,72 @@ int32_t qm_attention_combine(const float* partials, int32_t parts, int32_t rows,
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// The split-KV kernel needs scratch for its per-CTA partials.  The regular
+// entry point takes that scratch from the caller, who has to cudaMalloc it
+// somewhere.  Some hosts of this library cannot: a resident serving loop that
+// fixed its device-memory budget at start-up and runs the codec decoder on a
+// second stream (cudaMalloc and cudaFree synchronise the whole device and
+// would stall that stream in the middle of an audio packet), or an engine
+// whose allocator already owns all device memory.  For them the scratch below
+// is part of the library image: every GPU that loads the library carries
+// these bytes until the process exits, whether or not the entry point is used.
+constexpr int kStaticMaxBatch = 64;
+constexpr int kStaticMaxKvHeads = 8;
+constexpr size_t kStaticScratchBytes =
+    (size_t)(kMaxGrid + kStaticMaxBatch * kStaticMaxKvHeads) * 2 * kPartialStride * sizeof(float)   // partials
+    + (size_t)kStaticMaxBatch * kStaticMaxKvHeads * 2 * sizeof(int32_t)                             // first / last CTA
+    + 256;
+
+static __device__ __align__(256) unsigned char qm_static_decode_scratch[kStaticScratchBytes];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+// Device address of the scratch array on `device`.  In host code the array's
+// name is only a handle for the runtime, not something a kernel can be given,
+// so the address is looked up once per device (with that device current) and
+// remembered.
+int32_t static_scratch_address(int device, void** address_out) {
+    static std::mutex guard;
+    static void* known[kMaxDevices] = {};
+    if (device < 0 || device >= kMaxDevices) return qm_fail(QM_EINVAL, "device index out of range for the static scratch");
+    std::lock_guard<std::mutex> lock(guard);
+    if (!known[device]) {
+        int current = -1;
+        QM_CUDA_TRY(cudaGetDevice(&current), "get current device");
+        if (current != device)
+            return qm_fail(QM_EINVAL, "the pool's device must be current on the first qm_decode_attention_static call");
+        void* address = nullptr;
+        QM_CUDA_TRY(cudaGetSymbolAddress(&address, qm_static_decode_scratch), "look up static decode scratch");
+        if (!address) return qm_fail(QM_ECUDA, "static decode scratch has no device address");
+        known[device] = address;
+    }
+    *address_out = known[device];
+    return QM_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t qm_decode_attention_static(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot,
+                                              const int32_t* seq_lens, const int32_t* page_table,
+                                              int32_t max_pages, int32_t batch, int32_t q_heads, uint16_t* out,
+                                              void* stream) {
+    if (!pool) return qm_fail(QM_EINVAL, "pool is null");
+    if (batch > kStaticMaxBatch || pool->kv_heads > kStaticMaxKvHeads)
+        return qm_fail(QM_ECAPACITY,
+                       "qm_decode_attention_static handles at most 64 streams of at most 8 KV heads per call; "
+                       "use qm_decode_attention with caller-provided workspace for larger batches");
+    void* scratch = nullptr;
+    const int32_t looked_up = static_scratch_address(pool->device, &scratch);
+    if (looked_up != QM_OK) return looked_up;
+    // Nothing in the scratch has to start at zero: every partial slot and every
+    // first/last entry that the combine step reads is written earlier in the
+    // same call, so what the previous call left behind is never consumed.
+    return run_decode(pool, layer, q_rot, seq_lens, page_table, max_pages, batch, q_heads, out, nullptr, scratch,
+                      (int64_t)kStaticScratchBytes, static_cast<cudaStream_t>(stream), 0);
+}
