@@ -384,13 +384,17 @@ def cpu_baseline_and_parity(eng, q_rot0, out0, lengths, table):
 
 
 def main():
+    global LAYERS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=LAYERS,
+                    help="layers per step (default: the talker's 28); a smaller value gives a small case for profiling")
     args = ap.parse_args()
+    LAYERS = args.layers
     if args.impl == "reference":
         run_reference_arm(args)
     else:
