@@ -346,11 +346,93 @@ def run_ours(args):
 
     if rank == 0 and not args.no_cpu_baseline:
         line["cpu_baseline"], line["parity"] = cpu_baseline_and_parity(eng, q_rot[0], out[0], lengths, table)
+    eng.close()
+    del q, k, v, q_rot, out
+    torch.cuda.empty_cache()
+    if not args.no_prefill:
+        prefill = run_prefill_section(pkg, max(3, min(args.steps, 10)), args.warmup)
+        if world > 1:
+            t = torch.tensor([prefill["tflops"]], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t)
+            prefill["tflops_all_gpus"] = float(t.item())
+        line["prefill"] = prefill
     if rank == 0:
         print(json.dumps(line))
     eng.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def prefill_lengths():
+    """Prompt lengths of the prefill workload: 8 sequences, uniform in [1024, 8192], SplitMix64 seed 2."""
+    return splitmix64_ints(2 * 1000 + 99, 1024, 8192, 8)
+
+
+def run_prefill_section(pkg, steps, warmup):
+    """Secondary measurement: varlen causal prefill (fused append + tcgen05 attention), 1.7B talker shape."""
+    import torch
+
+    lengths = prefill_lengths()
+    cu = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    total = int(cu[-1])
+    pages_per_seq = (lengths + PAGE - 1) // PAGE
+    max_pages = int(pages_per_seq.max())
+    num_pages = int(pages_per_seq.sum())
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(2000)
+    eng = pkg.TalkerAttention(layers=1, num_pages=num_pages, q_heads=Q_HEADS, kv_heads=KV_HEADS,
+                              max_positions=int(lengths.max()))
+    perm = torch.randperm(num_pages, generator=gen, device="cuda").to(torch.int32).cpu().numpy()
+    table = np.zeros((len(lengths), max_pages), dtype=np.int32)
+    cursor = 0
+    for s, n in enumerate(pages_per_seq):
+        table[s, :n] = perm[cursor:cursor + n]
+        cursor += int(n)
+    page_table = torch.from_numpy(table).cuda()
+    cu_dev = torch.from_numpy(cu).cuda()
+    q = torch.randn(total, Q_HEADS, D, generator=gen, device="cuda").to(torch.bfloat16)
+    k = torch.randn(total, KV_HEADS, D, generator=gen, device="cuda").to(torch.bfloat16)
+    v = torch.randn(total, KV_HEADS, D, generator=gen, device="cuda").to(torch.bfloat16)
+    ones = torch.ones(D, dtype=torch.bfloat16, device="cuda")
+    q_rot = torch.empty_like(q)
+    out = torch.empty_like(q)
+    max_len = int(lengths.max())
+
+    def step():
+        eng.prefill_norm_rope_scatter(0, q, k, v, ones, ones, cu_dev, page_table, q_rot=q_rot)
+        eng.launch_attention_prefill(0, q_rot, cu_dev, page_table, max_len, out=out)
+
+    for _ in range(max(warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    append_ms, attn_ms = [], []
+    for _ in range(steps):
+        e[0].record()
+        eng.prefill_norm_rope_scatter(0, q, k, v, ones, ones, cu_dev, page_table, q_rot=q_rot)
+        e[1].record()
+        eng.launch_attention_prefill(0, q_rot, cu_dev, page_table, max_len, out=out)
+        e[2].record()
+        torch.cuda.synchronize()
+        append_ms.append(e[0].elapsed_time(e[1]))
+        attn_ms.append(e[1].elapsed_time(e[2]))
+    status = eng.status()
+    flops = float(sum(4096 * int(n) * (int(n) + 1) for n in lengths))
+    attn = float(np.mean(attn_ms))
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    burst = float(peaks.get("bf16_tflops", 1590.0))
+    sustained = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    tflops = flops / (attn * 1e-3) / 1e12
+    result = {
+        "workload": "varlen_causal_prefill_b8", "prompt_lengths": [int(n) for n in lengths], "tokens": total,
+        "algorithmic_flops": flops, "attention_ms": attn, "attention_ms_min": float(np.min(attn_ms)),
+        "append_ms": float(np.mean(append_ms)), "tflops": tflops,
+        "frac_of_measured_burst_peak": tflops / burst, "frac_of_measured_sustained_peak": tflops / sustained,
+        "peak_tflops_burst": burst, "peak_tflops_sustained": sustained, "device_status": status,
+        "append_gbs": total * (Q_HEADS + 2 * KV_HEADS) * D * 2 * 2 / (float(np.mean(append_ms)) * 1e-3) / 1e9,
+    }
+    eng.close()
+    return result
 
 
 def cpu_baseline_and_parity(eng, q_rot0, out0, lengths, table):
@@ -391,6 +473,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the secondary prefill measurement")
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="layers per step (default: the talker's 28); a smaller value gives a small case for profiling")
     args = ap.parse_args()

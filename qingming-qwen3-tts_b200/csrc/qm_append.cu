@@ -69,17 +69,18 @@ __device__ __forceinline__ float reference_order_sum_of_squares(float s0, float 
     return __fadd_rn(__fadd_rn(w0, w2), __fadd_rn(w1, w3));
 }
 
+// R consecutive head rows of the same token per warp (R divides q_heads + kv_heads): one stream / position
+// lookup and R independent 256-byte loads in flight per warp.
+template <int R>
 __global__ void __launch_bounds__(kAppendWarps * 32) qm_norm_rope_append_kernel(const AppendArgs a) {
     const int lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * kAppendWarps + (threadIdx.x >> 5);
-    if (row >= a.rows_total) return;
+    const long long row0 = ((long long)blockIdx.x * kAppendWarps + (threadIdx.x >> 5)) * R;
+    if (row0 >= a.rows_total) return;
     const int heads = a.q_heads + a.kv_heads;
-    const int token = (int)(row / heads);
-    const int slot = (int)(row % heads);
-    const bool is_query = slot < a.q_heads;
-    const int head = is_query ? slot : slot - a.q_heads;
+    const int token = (int)(row0 / heads);
+    const int slot0 = (int)(row0 % heads);
 
-    // Which stream and position this packed row belongs to.
+    // Which stream and position this packed token belongs to.
     int stream, position;
     if (a.cu_seqlens == nullptr) {
         stream = token;
@@ -99,57 +100,78 @@ __global__ void __launch_bounds__(kAppendWarps * 32) qm_norm_rope_append_kernel(
         return;
     }
 
-    const uint16_t* source = is_query ? a.q + ((size_t)token * a.q_heads + head) * kHeadDim
-                                      : a.k + ((size_t)token * a.kv_heads + head) * kHeadDim;
-    const uint2 raw = *reinterpret_cast<const uint2*>(source + 4 * lane);
-    const uint2 wraw = *reinterpret_cast<const uint2*>((is_query ? a.q_norm_weight : a.k_norm_weight) + 4 * lane);
+    uint2 raw[R], vraw[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int slot = slot0 + r;
+        const bool is_query = slot < a.q_heads;
+        const int head = is_query ? slot : slot - a.q_heads;
+        const uint16_t* source = is_query ? a.q + ((size_t)token * a.q_heads + head) * kHeadDim
+                                          : a.k + ((size_t)token * a.kv_heads + head) * kHeadDim;
+        raw[r] = *reinterpret_cast<const uint2*>(source + 4 * lane);
+        vraw[r] = is_query ? make_uint2(0u, 0u)
+                           : *reinterpret_cast<const uint2*>(a.v + ((size_t)token * a.kv_heads + head) * kHeadDim + 4 * lane);
+    }
+    const uint2 qwraw = *reinterpret_cast<const uint2*>(a.q_norm_weight + 4 * lane);
+    const uint2 kwraw = *reinterpret_cast<const uint2*>(a.k_norm_weight + 4 * lane);
     const uint2 craw = *reinterpret_cast<const uint2*>(a.rope_cos + (size_t)position * kHeadDim + 4 * lane);
     const uint2 sraw = *reinterpret_cast<const uint2*>(a.rope_sin + (size_t)position * kHeadDim + 4 * lane);
-
-    float x[4] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y)};
-    const float w[4] = {bf16_lo(wraw.x), bf16_hi(wraw.x), bf16_lo(wraw.y), bf16_hi(wraw.y)};
     const float c[4] = {bf16_lo(craw.x), bf16_hi(craw.x), bf16_lo(craw.y), bf16_hi(craw.y)};
     const float s[4] = {bf16_lo(sraw.x), bf16_hi(sraw.x), bf16_lo(sraw.y), bf16_hi(sraw.y)};
 
-    const float sum = reference_order_sum_of_squares(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]),
-                                                     __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
-    const float inverse_rms = rsqrtf(__fadd_rn(__fdiv_rn(sum, (float)kHeadDim), a.epsilon));
+    // Where this token's K/V rows go (same page and slot for every KV head).
+    long long kv_row = -1;          // ((page * kv_heads) * 64 + slot) in rows of 128, head added below
+    if (slot0 + R > a.q_heads) {
+        if (position >= a.max_pages * kPageTokens) {
+            if (lane == 0) atomicOr(a.status, QM_DEVSTAT_BAD_POS);
+        } else {
+            const int page = a.page_table[(size_t)stream * a.max_pages + (position >> 6)];
+            if (page < 0 || page >= a.num_pages) {
+                if (lane == 0) atomicOr(a.status, QM_DEVSTAT_BAD_PAGE);
+            } else {
+                kv_row = (long long)page * a.kv_heads * kPageTokens + (position & 63);
+            }
+        }
+    }
 
-    // RMSNorm: normalise in fp32 -> bf16 -> multiply by the bf16 weight -> bf16.
-    float n[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) n[i] = round_bf16(__fmul_rn(round_bf16(__fmul_rn(x[i], inverse_rms)), w[i]));
+    for (int r = 0; r < R; ++r) {
+        const int slot = slot0 + r;
+        const bool is_query = slot < a.q_heads;
+        const int head = is_query ? slot : slot - a.q_heads;
+        const uint2 wraw = is_query ? qwraw : kwraw;
+        const float x[4] = {bf16_lo(raw[r].x), bf16_hi(raw[r].x), bf16_lo(raw[r].y), bf16_hi(raw[r].y)};
+        const float w[4] = {bf16_lo(wraw.x), bf16_hi(wraw.x), bf16_lo(wraw.y), bf16_hi(wraw.y)};
 
-    // rotate_half: dimension d pairs with d +- 64, which lane l ^ 16 holds.
-    uint32_t out_bits[4];
+        const float sum = reference_order_sum_of_squares(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]),
+                                                         __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
+        const float inverse_rms = rsqrtf(__fadd_rn(__fdiv_rn(sum, (float)kHeadDim), a.epsilon));
+
+        // RMSNorm: normalise in fp32 -> bf16 -> multiply by the bf16 weight -> bf16.
+        float n[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float partner = __shfl_xor_sync(0xffffffffu, n[i], 16);
-        if (lane < 16) partner = -partner;
-        const float first = round_bf16(__fmul_rn(n[i], c[i]));
-        const float second = round_bf16(__fmul_rn(partner, s[i]));
-        out_bits[i] = f32_to_bf16_bits(__fadd_rn(first, second));
-    }
-    const uint2 packed = make_uint2(out_bits[0] | (out_bits[1] << 16), out_bits[2] | (out_bits[3] << 16));
+        for (int i = 0; i < 4; ++i) n[i] = round_bf16(__fmul_rn(round_bf16(__fmul_rn(x[i], inverse_rms)), w[i]));
 
-    if (is_query) {
-        *reinterpret_cast<uint2*>(a.q_rot + ((size_t)token * a.q_heads + head) * kHeadDim + 4 * lane) = packed;
-        return;
-    }
+        // rotate_half: dimension d pairs with d +- 64, which lane l ^ 16 holds.
+        uint32_t out_bits[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float partner = __shfl_xor_sync(0xffffffffu, n[i], 16);
+            if (lane < 16) partner = -partner;
+            const float first = round_bf16(__fmul_rn(n[i], c[i]));
+            const float second = round_bf16(__fmul_rn(partner, s[i]));
+            out_bits[i] = f32_to_bf16_bits(__fadd_rn(first, second));
+        }
+        const uint2 packed = make_uint2(out_bits[0] | (out_bits[1] << 16), out_bits[2] | (out_bits[3] << 16));
 
-    if (position >= a.max_pages * kPageTokens) {
-        if (lane == 0) atomicOr(a.status, QM_DEVSTAT_BAD_POS);
-        return;
+        if (is_query) {
+            *reinterpret_cast<uint2*>(a.q_rot + ((size_t)token * a.q_heads + head) * kHeadDim + 4 * lane) = packed;
+        } else if (kv_row >= 0) {
+            const size_t dst = ((size_t)kv_row + (size_t)head * kPageTokens) * kHeadDim + 4 * lane;
+            *reinterpret_cast<uint2*>(a.key_pool + dst) = packed;
+            *reinterpret_cast<uint2*>(a.value_pool + dst) = vraw[r];
+        }
     }
-    const int page = a.page_table[(size_t)stream * a.max_pages + (position >> 6)];
-    if (page < 0 || page >= a.num_pages) {
-        if (lane == 0) atomicOr(a.status, QM_DEVSTAT_BAD_PAGE);
-        return;
-    }
-    const size_t dst = (((size_t)page * a.kv_heads + head) * kPageTokens + (position & 63)) * kHeadDim + 4 * lane;
-    *reinterpret_cast<uint2*>(a.key_pool + dst) = packed;
-    *reinterpret_cast<uint2*>(a.value_pool + dst) =
-        *reinterpret_cast<const uint2*>(a.v + ((size_t)token * a.kv_heads + head) * kHeadDim + 4 * lane);
 }
 
 int32_t launch_append(qm_kv_pool* pool, int32_t layer, const AppendArgs& proto, long long tokens, cudaStream_t stream) {
@@ -161,9 +183,17 @@ int32_t launch_append(qm_kv_pool* pool, int32_t layer, const AppendArgs& proto, 
     a.kv_heads = pool->kv_heads;
     a.rows_total = tokens * (a.q_heads + a.kv_heads);
     if (a.rows_total == 0) return QM_OK;
-    const long long blocks = (a.rows_total + kAppendWarps - 1) / kAppendWarps;
+    const int heads = a.q_heads + a.kv_heads;
+    const int rows_per_warp = heads % 4 == 0 ? 4 : (heads % 2 == 0 ? 2 : 1);
+    const long long warps = (a.rows_total + rows_per_warp - 1) / rows_per_warp;
+    const long long blocks = (warps + kAppendWarps - 1) / kAppendWarps;
     if (blocks > 0x7fffffffLL) return qm_fail(QM_ECAPACITY, "too many rows for one append launch");
-    qm_norm_rope_append_kernel<<<(unsigned)blocks, kAppendWarps * 32, 0, stream>>>(a);
+    if (rows_per_warp == 4)
+        qm_norm_rope_append_kernel<4><<<(unsigned)blocks, kAppendWarps * 32, 0, stream>>>(a);
+    else if (rows_per_warp == 2)
+        qm_norm_rope_append_kernel<2><<<(unsigned)blocks, kAppendWarps * 32, 0, stream>>>(a);
+    else
+        qm_norm_rope_append_kernel<1><<<(unsigned)blocks, kAppendWarps * 32, 0, stream>>>(a);
     QM_CUDA_TRY(cudaGetLastError(), "QK norm/RoPE/cache launch");
     return QM_OK;
 }

@@ -5,6 +5,7 @@
 
 #include <cuda_runtime.h>
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <stdint.h>
 
 #include "../../include/qm_attention.h"
@@ -58,6 +59,12 @@ __device__ __forceinline__ float round_bf16(float v) { return bf16_bits_to_f32(f
 // Low / high bf16 of a packed pair, widened.
 __device__ __forceinline__ float bf16_lo(uint32_t pair) { return __uint_as_float(pair << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t pair) { return __uint_as_float(pair & 0xffff0000u); }
+
+// Two floats -> packed bf16x2 (a in the low half), round-to-nearest-even, one cvt instruction.
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;

@@ -1,0 +1,134 @@
+"""GPU parity of the prefill path: fused varlen norm + RoPE + paged append, then tcgen05 causal attention.
+
+The append must equal the oracle's bit-faithful mode up to the rsqrtf ulp cases (and equals the reference
+kernels' bits in test_golden_gpu.py); attention is compared with the fp32 oracle under the stated bf16 tolerance
+(max-abs <= 2e-2, mean-relative <= 1e-2) and with the reference kernels' own output from the golden file.
+"""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import qm_oracle as oracle
+import scenario
+from golden.make_reference_golden import PREFILL_CASES
+
+pytestmark = pytest.mark.gpu
+TOL_MAX_ABS = 2e-2
+TOL_MEAN_REL = 1e-2
+GOLDEN = np.load(Path(__file__).resolve().parent / "golden" / "reference_kernels_golden.npz")
+
+
+def ulp_distance(a, b):
+    def key(x):
+        x = x.astype(np.int32)
+        return np.where(x & 0x8000, 0x8000 - (x & 0x7FFF), 0x8000 + (x & 0x7FFF))
+    return np.abs(key(a) - key(b))
+
+
+def assert_roped_close(got, want):
+    # device rsqrtf vs the oracle's 1/sqrtf flips the first rounding of a few rows; after RoPE's a*cos + b*sin
+    # the flipped ulp is an absolute error of at most one ulp of the normalised value (|x| < 8 -> 2^-5)
+    if got.size == 0:
+        return
+    diff = np.abs(oracle.bf16_to_f32(got) - oracle.bf16_to_f32(want))
+    assert diff.max() <= 2.0 ** -5, diff.max()
+    assert (got != want).mean() <= 1e-3, (got != want).mean()
+
+
+def check_append(ps, got):
+    q_rot, kcs, vcs = ps.expected_append()
+    assert_roped_close(got["q_rot"], q_rot)
+    for s in range(ps.batch):
+        n = int(ps.lengths[s])
+        gk = oracle.gather_paged(got["key_pool"], ps.page_table[s], n, ps.max_cache)
+        gv = oracle.gather_paged(got["value_pool"], ps.page_table[s], n, ps.max_cache)
+        assert np.array_equal(gv[:, :n], vcs[s][:, :n]), "V rows / page indexing must be bit-exact"
+        assert_roped_close(gk[:, :n], kcs[s][:, :n])
+
+
+def check_prefill(qm, ps, rows_per_stream=None):
+    got = scenario.run_prefill_on_gpu(qm, ps)
+    assert got["status"] == 0
+    check_append(ps, got)
+    want, mask = ps.expected_attention(mode="fp32", rows_per_stream=rows_per_stream)
+    m = oracle.error_metrics(oracle.bf16_to_f32(got["out"])[mask], want[mask])
+    assert m["max_abs"] <= TOL_MAX_ABS and m["mean_rel"] <= TOL_MEAN_REL, m
+    return m, got
+
+
+@pytest.mark.parametrize("lengths", [[70], [128], [129], [1], [1, 2, 3], [64, 65, 127], [300, 257, 64, 5]])
+def test_small_sequences(qm, lengths):
+    check_prefill(qm, scenario.PrefillScenario(seed=40 + len(lengths) + lengths[0], lengths=lengths, random_weights=True))
+
+
+def test_unshuffled_pages_and_unit_weights(qm):
+    check_prefill(qm, scenario.PrefillScenario(seed=3, lengths=[200, 131], shuffle_pages=False))
+
+
+def test_one_long_sequence(qm):
+    m, _ = check_prefill(qm, scenario.PrefillScenario(seed=2, lengths=[1500]))
+    print("prefill L=1500", m)
+
+
+def test_ragged_batch_sampled_rows(qm):
+    # the config-3 shape at reduced lengths; the oracle checks the first and last 96 rows of every sequence
+    lengths = [int(x) for x in oracle.uniform_int(2 * 1000 + 99, 1024, 3000, 4)]
+    ps = scenario.PrefillScenario(seed=2, lengths=lengths)
+    got = scenario.run_prefill_on_gpu(qm, ps)
+    assert got["status"] == 0
+    for part in ("head", "tail"):
+        rows = {s: ((0, 96) if part == "head" else (n - 96, n)) for s, n in enumerate(lengths)}
+        want, mask = ps.expected_attention(mode="fp32", rows_per_stream=rows)
+        m = oracle.error_metrics(oracle.bf16_to_f32(got["out"])[mask], want[mask])
+        assert m["max_abs"] <= TOL_MAX_ABS and m["mean_rel"] <= TOL_MEAN_REL, (part, m)
+
+
+def test_empty_sequence_in_batch(qm):
+    check_prefill(qm, scenario.PrefillScenario(seed=5, lengths=[0, 40, 0, 129]))
+
+
+@pytest.mark.parametrize("name", sorted(PREFILL_CASES))
+def test_attention_against_reference_kernel_output(qm, name):
+    seed, lengths, rw = PREFILL_CASES[name]
+    ps = scenario.PrefillScenario(seed=seed, lengths=lengths, random_weights=rw)
+    got = scenario.run_prefill_on_gpu(qm, ps)
+    m = oracle.error_metrics(oracle.bf16_to_f32(got["out"]), oracle.bf16_to_f32(GOLDEN[f"{name}_context"]))
+    assert m["max_abs"] <= TOL_MAX_ABS and m["mean_rel"] <= TOL_MEAN_REL, m
+
+
+def test_prefill_then_decode_share_the_cache(qm):
+    """Prefill writes the pages, a decode step then attends over them plus its own token."""
+    import torch
+
+    ps = scenario.PrefillScenario(seed=9, lengths=[100, 63], spare_pages=4)
+    q_rot, kcs, vcs = ps.expected_append()
+    eng = qm.TalkerAttention(layers=1, num_pages=ps.num_pages, max_positions=256)
+    try:
+        tb = scenario._bf16_tensor
+        cu = torch.from_numpy(ps.cu_seqlens).cuda()
+        # give stream 1 (63 tokens) room for position 63: still page 0; stream 0 position 100: page 1
+        table = torch.from_numpy(np.maximum(ps.page_table, 0)).cuda()
+        eng.prefill_norm_rope_scatter(0, tb(torch, ps.q), tb(torch, ps.k), tb(torch, ps.v), tb(torch, ps.q_w),
+                                      tb(torch, ps.k_w), cu, table)
+        newq = oracle.normal_bf16(991, (2, 16, 128))
+        newk = oracle.normal_bf16(992, (2, 8, 128))
+        newv = oracle.normal_bf16(993, (2, 8, 128))
+        positions = torch.from_numpy(ps.lengths).cuda()
+        qr = eng.launch_qk_norm_rope_cache_m1(0, tb(torch, newq), tb(torch, newk), tb(torch, newv), tb(torch, ps.q_w),
+                                              tb(torch, ps.k_w), positions, table)
+        out = eng.launch_attention(0, qr, torch.from_numpy(ps.lengths + 1).cuda(), table)
+        torch.cuda.synchronize()
+        assert eng.status() == 0
+        cos, sin = oracle.make_rope(256)
+        want_rows = []
+        for s in range(2):
+            pos = int(ps.lengths[s])
+            kc, vc = kcs[s].copy(), vcs[s].copy()
+            qrs = oracle.append(newq[s:s + 1], newk[s:s + 1], newv[s:s + 1], ps.q_w, ps.k_w, cos[pos:pos + 1],
+                                sin[pos:pos + 1], pos, kc, vc)
+            want_rows.append(oracle.decode_attention(qrs, [kc], [vc], [pos + 1], mode="fp32")[0])
+        m = oracle.error_metrics(oracle.bf16_to_f32(scenario._bits(out)), np.stack(want_rows))
+        assert m["max_abs"] <= TOL_MAX_ABS and m["mean_rel"] <= TOL_MEAN_REL, m
+    finally:
+        eng.close()
