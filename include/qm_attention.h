@@ -110,6 +110,20 @@ int32_t qm_decode_append_rope(qm_kv_pool* pool, int32_t layer, const uint16_t* q
                               const int32_t* positions, const int32_t* page_table, int32_t max_pages,
                               int32_t batch, int32_t q_heads, float epsilon, uint16_t* q_rot, void* stream);
 
+/* The same decode step when this pool holds only a slice of each stream (a very
+ * long context split across GPUs): launch_qk_norm_rope_cache_m1 (17.cu:17741)
+ * with the RoPE row and the cache slot given separately.  positions[batch] is
+ * the absolute position (RoPE row); cache_positions[batch] is the slot index
+ * inside THIS pool's slice, or -1 on a rank that does not own the new token
+ * (q_rot is still produced, K/V are not written). */
+int32_t qm_decode_append_rope_sliced(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const uint16_t* k,
+                                     const uint16_t* v, const uint16_t* q_norm_weight,
+                                     const uint16_t* k_norm_weight, const uint16_t* rope_cos,
+                                     const uint16_t* rope_sin, int32_t rope_rows, const int32_t* positions,
+                                     const int32_t* cache_positions, const int32_t* page_table,
+                                     int32_t max_pages, int32_t batch, int32_t q_heads, float epsilon,
+                                     uint16_t* q_rot, void* stream);
+
 /* Prefill, packed varlen: the launch_rmsnorm x2 + launch_rope_rows x2 +
  * scatter_prefill_cache sequence of prefill() (17.cu:16763-16798) in one
  * kernel.  Sequence s owns packed rows cu_seqlens[s] .. cu_seqlens[s+1]-1 and

@@ -56,6 +56,9 @@ ABI = {
     "qm_rope_table_fill": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_double, c_void_p]),
     "qm_decode_append_rope": (c_int32, [c_void_p, c_int32] + [c_void_p] * 7 + [c_int32, c_void_p, c_void_p, c_int32,
                                                                            c_int32, c_int32, c_float, c_void_p, c_void_p]),
+    "qm_decode_append_rope_sliced": (c_int32, [c_void_p, c_int32] + [c_void_p] * 7 + [c_int32, c_void_p, c_void_p, c_void_p,
+                                                                                  c_int32, c_int32, c_int32, c_float, c_void_p,
+                                                                                  c_void_p]),
     "qm_prefill_append_rope_varlen": (c_int32, [c_void_p, c_int32] + [c_void_p] * 7 +
                                       [c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                        c_float, c_void_p, c_void_p]),
@@ -187,6 +190,20 @@ class TalkerAttention:
             self.pool, layer, _ptr(q), _ptr(k), _ptr(v), _ptr(q_norm_weight), _ptr(k_norm_weight),
             _ptr(self.rope_cos), _ptr(self.rope_sin), self.max_positions, _ptr(positions), _ptr(page_table),
             page_table.shape[1], batch, self.q_heads, self.epsilon, _ptr(q_rot), _stream()))
+        return q_rot
+
+    def launch_qk_norm_rope_cache_m1_sliced(self, layer, q, k, v, q_norm_weight, k_norm_weight, positions,
+                                            cache_positions, page_table, q_rot=None):
+        """Decode append when this pool holds a slice of each stream: RoPE row and cache slot given separately."""
+        import torch
+
+        batch = q.shape[0]
+        if q_rot is None:
+            q_rot = torch.empty_like(q)
+        _check(self.lib.qm_decode_append_rope_sliced(
+            self.pool, layer, _ptr(q), _ptr(k), _ptr(v), _ptr(q_norm_weight), _ptr(k_norm_weight),
+            _ptr(self.rope_cos), _ptr(self.rope_sin), self.max_positions, _ptr(positions), _ptr(cache_positions),
+            _ptr(page_table), page_table.shape[1], batch, self.q_heads, self.epsilon, _ptr(q_rot), _stream()))
         return q_rot
 
     def prefill_norm_rope_scatter(self, layer, q, k, v, q_norm_weight, k_norm_weight, cu_seqlens, page_table,

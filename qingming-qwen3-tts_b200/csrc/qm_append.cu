@@ -30,6 +30,7 @@ struct AppendArgs {
     const uint16_t* rope_sin;
     const int32_t* positions;     // decode: [batch]; prefill: start_positions or null
     const int32_t* cu_seqlens;    // null for decode
+    const int32_t* cache_positions;   // decode only, optional: slot index in this pool (-1: do not append here)
     const int32_t* page_table;
     uint16_t* q_rot;
     uint16_t* key_pool;
@@ -122,14 +123,19 @@ __global__ void __launch_bounds__(kAppendWarps * 32) qm_norm_rope_append_kernel(
     // Where this token's K/V rows go (same page and slot for every KV head).
     long long kv_row = -1;          // ((page * kv_heads) * 64 + slot) in rows of 128, head added below
     if (slot0 + R > a.q_heads) {
-        if (position >= a.max_pages * kPageTokens) {
+        // The RoPE row is the absolute position; the cache slot may be given separately when this pool
+        // holds only a slice of the stream.
+        const int cache_pos = a.cache_positions ? a.cache_positions[stream] : position;
+        if (cache_pos < 0) {
+            // this rank does not own the new token
+        } else if (cache_pos >= a.max_pages * kPageTokens) {
             if (lane == 0) atomicOr(a.status, QM_DEVSTAT_BAD_POS);
         } else {
-            const int page = a.page_table[(size_t)stream * a.max_pages + (position >> 6)];
+            const int page = a.page_table[(size_t)stream * a.max_pages + (cache_pos >> 6)];
             if (page < 0 || page >= a.num_pages) {
                 if (lane == 0) atomicOr(a.status, QM_DEVSTAT_BAD_PAGE);
             } else {
-                kv_row = (long long)page * a.kv_heads * kPageTokens + (position & 63);
+                kv_row = (long long)page * a.kv_heads * kPageTokens + (cache_pos & 63);
             }
         }
     }
@@ -200,15 +206,11 @@ int32_t launch_append(qm_kv_pool* pool, int32_t layer, const AppendArgs& proto, 
 
 bool misaligned8(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) != 0; }
 
-}  // namespace
-
-extern "C" {
-
-int32_t qm_decode_append_rope(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const uint16_t* k,
-                              const uint16_t* v, const uint16_t* q_norm_weight, const uint16_t* k_norm_weight,
-                              const uint16_t* rope_cos, const uint16_t* rope_sin, int32_t rope_rows,
-                              const int32_t* positions, const int32_t* page_table, int32_t max_pages,
-                              int32_t batch, int32_t q_heads, float epsilon, uint16_t* q_rot, void* stream) {
+int32_t decode_append(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                      const uint16_t* q_norm_weight, const uint16_t* k_norm_weight, const uint16_t* rope_cos,
+                      const uint16_t* rope_sin, int32_t rope_rows, const int32_t* positions,
+                      const int32_t* cache_positions, const int32_t* page_table, int32_t max_pages, int32_t batch,
+                      int32_t q_heads, float epsilon, uint16_t* q_rot, void* stream) {
     if (!pool) return qm_fail(QM_EINVAL, "pool is null");
     if (layer < 0 || layer >= pool->layers) return qm_fail(QM_EINVAL, "layer out of range");
     if (!q || !k || !v || !q_norm_weight || !k_norm_weight || !rope_cos || !rope_sin || !positions || !page_table ||
@@ -223,9 +225,35 @@ int32_t qm_decode_append_rope(qm_kv_pool* pool, int32_t layer, const uint16_t* q
     a.q_norm_weight = q_norm_weight; a.k_norm_weight = k_norm_weight;
     a.rope_cos = rope_cos; a.rope_sin = rope_sin;
     a.positions = positions; a.cu_seqlens = nullptr; a.page_table = page_table;
+    a.cache_positions = cache_positions;
     a.q_rot = q_rot;
     a.rope_rows = rope_rows; a.max_pages = max_pages; a.batch = batch; a.q_heads = q_heads; a.epsilon = epsilon;
     return launch_append(pool, layer, a, batch, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t qm_decode_append_rope(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const uint16_t* k,
+                              const uint16_t* v, const uint16_t* q_norm_weight, const uint16_t* k_norm_weight,
+                              const uint16_t* rope_cos, const uint16_t* rope_sin, int32_t rope_rows,
+                              const int32_t* positions, const int32_t* page_table, int32_t max_pages,
+                              int32_t batch, int32_t q_heads, float epsilon, uint16_t* q_rot, void* stream) {
+    return decode_append(pool, layer, q, k, v, q_norm_weight, k_norm_weight, rope_cos, rope_sin, rope_rows, positions,
+                         nullptr, page_table, max_pages, batch, q_heads, epsilon, q_rot, stream);
+}
+
+int32_t qm_decode_append_rope_sliced(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const uint16_t* k,
+                                     const uint16_t* v, const uint16_t* q_norm_weight,
+                                     const uint16_t* k_norm_weight, const uint16_t* rope_cos,
+                                     const uint16_t* rope_sin, int32_t rope_rows, const int32_t* positions,
+                                     const int32_t* cache_positions, const int32_t* page_table,
+                                     int32_t max_pages, int32_t batch, int32_t q_heads, float epsilon,
+                                     uint16_t* q_rot, void* stream) {
+    if (!cache_positions) return qm_fail(QM_EINVAL, "cache_positions is null");
+    return decode_append(pool, layer, q, k, v, q_norm_weight, k_norm_weight, rope_cos, rope_sin, rope_rows, positions,
+                         cache_positions, page_table, max_pages, batch, q_heads, epsilon, q_rot, stream);
 }
 
 int32_t qm_prefill_append_rope_varlen(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const uint16_t* k,

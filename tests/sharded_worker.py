@@ -1,0 +1,65 @@
+"""One NCCL rank of the split-across-GPUs decode check (launched by torchrun; see test_sharded_gpu.py)."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+import __graft_entry__ as entry  # noqa: E402
+import scenario  # noqa: E402
+import sharded_helpers  # noqa: E402
+from oracle import qm_oracle as oracle  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    qm = entry.load_package()
+    qm.load_library()
+    import importlib
+
+    sh = importlib.import_module("qingming_qwen3_tts_b200.sharded")
+    sc = scenario.DecodeScenario(seed=63, lengths=[8191] * 4)      # the long-context shape at reduced length
+    exp = sc.expected()
+    st = sharded_helpers.rank_local_state(sc, exp, sh, world, rank, include_new_token=False)
+    tb = scenario._bf16_tensor
+    eng = qm.TalkerAttention(layers=1, num_pages=st["num_pages"], max_positions=sc.max_pos)
+    kview, vview = eng.pool_view(0)
+    kview.copy_(tb(torch, st["kpool"]))
+    vview.copy_(tb(torch, st["vpool"]))
+    owner = rank == world - 1
+    cache_pos = (sc.lengths - st["begins"]).astype(np.int32) if owner else np.full(sc.batch, -1, dtype=np.int32)
+    table = torch.from_numpy(st["table"]).cuda()
+    q_rot = eng.launch_qk_norm_rope_cache_m1_sliced(
+        0, tb(torch, sc.q), tb(torch, sc.k), tb(torch, sc.v), tb(torch, sc.q_w), tb(torch, sc.k_w),
+        torch.from_numpy(sc.lengths).cuda(), torch.from_numpy(cache_pos).cuda(), table)
+    local_lens = st["local_lens"] + (1 if owner else 0)
+    runner = sh.ShardedDecode()
+    out = sh.sharded_decode_attention(eng, runner, 0, q_rot, torch.from_numpy(local_lens.astype(np.int32)).cuda(), table)
+    torch.cuda.synchronize()
+    assert eng.status() == 0
+    bits = scenario._bits(out)
+    m = oracle.error_metrics(oracle.bf16_to_f32(bits), exp["out_fp32"])
+    assert m["max_abs"] <= 2e-2 and m["mean_rel"] <= 1e-2, m
+    # every rank must hold the same bits
+    mine = out.view(torch.int16).to(torch.int64).sum().reshape(1)
+    sums = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(sums, mine)
+    assert all(int(x) == int(sums[0]) for x in sums)
+    eng.close()
+    dist.barrier()
+    if rank == 0:
+        print("SHARDED_OK", m)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
