@@ -356,6 +356,8 @@ def run_ours(args):
             dist.all_reduce(t)
             prefill["tflops_all_gpus"] = float(t.item())
         line["prefill"] = prefill
+    if not args.no_long_context:
+        line["long_context"] = run_long_context_section(pkg, world, rank, args.steps)
     if rank == 0:
         print(json.dumps(line))
     eng.close()
@@ -435,6 +437,67 @@ def run_prefill_section(pkg, steps, warmup):
     return result
 
 
+def run_long_context_section(pkg, world, rank, steps):
+    """Secondary measurement: 4 streams of 65 536 keys each, keys split contiguously over the ranks; per layer every
+    rank runs the split-KV kernel on its slice, the (m, l, o) partials are all-gathered and combined."""
+    import importlib
+
+    import torch
+    import torch.distributed as dist
+
+    sh = importlib.import_module("qingming_qwen3_tts_b200.sharded")
+    streams, length, layers = 4, 65536, 4
+    begin, end = sh.slice_bounds(length, world, rank)
+    local = end - begin
+    pages_per_stream = (local + PAGE - 1) // PAGE
+    num_pages = streams * pages_per_stream
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(3000 + rank)
+    eng = pkg.TalkerAttention(layers=layers, num_pages=num_pages, q_heads=Q_HEADS, kv_heads=KV_HEADS, max_positions=64)
+    for layer in range(layers):
+        for view in eng.pool_view(layer):
+            view.normal_(generator=gen)
+    perm = torch.randperm(num_pages, generator=gen, device="cuda").to(torch.int32)
+    page_table = perm.view(streams, pages_per_stream).contiguous()
+    seq_lens = torch.full((streams,), local, dtype=torch.int32, device="cuda")
+    q_rot = torch.randn(streams, Q_HEADS, D, generator=gen, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q_rot)
+    if world > 1:
+        runner = sh.ShardedDecode()
+
+    def one_layer(layer):
+        if world > 1:
+            sh.sharded_decode_attention(eng, runner, layer, q_rot, seq_lens, page_table, out=out)
+        else:
+            eng.launch_attention(layer, q_rot, seq_lens, page_table, out=out)
+
+    for i in range(8):
+        one_layer(i % layers)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    iters = max(steps, 5) * layers
+    start.record()
+    for i in range(iters):
+        one_layer(i % layers)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / iters
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    status = eng.status()
+    eng.close()
+    total_bytes = streams * length * 4096
+    peak, _ = load_peaks()
+    return {"workload": "long_context_split_kv_b4_l65536", "streams": streams, "kv_len": length, "gpus": world,
+            "us_per_layer": ms * 1e3, "aggregate_gbs": total_bytes / (ms * 1e-3) / 1e9,
+            "frac_of_measured_hbm_peak_per_gpu": total_bytes / world / (ms * 1e-3) / 1e9 / peak,
+            "exchange_bytes_per_rank": streams * Q_HEADS * 130 * 4 if world > 1 else 0, "device_status": status}
+
+
 def cpu_baseline_and_parity(eng, q_rot0, out0, lengths, table):
     """CPU-baseline leg: times the oracle on a sample of layer 0 and uses its fp32 mode to check the GPU result."""
     import torch
@@ -474,6 +537,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the secondary prefill measurement")
+    ap.add_argument("--no-long-context", action="store_true", help="skip the secondary split-KV long-context measurement")
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="layers per step (default: the talker's 28); a smaller value gives a small case for profiling")
     args = ap.parse_args()

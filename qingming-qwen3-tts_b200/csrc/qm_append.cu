@@ -74,6 +74,8 @@ __device__ __forceinline__ float reference_order_sum_of_squares(float s0, float 
 // lookup and R independent 256-byte loads in flight per warp.
 template <int R>
 __global__ void __launch_bounds__(kAppendWarps * 32) qm_norm_rope_append_kernel(const AppendArgs a) {
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const long long row0 = ((long long)blockIdx.x * kAppendWarps + (threadIdx.x >> 5)) * R;
     if (row0 >= a.rows_total) return;
@@ -194,12 +196,13 @@ int32_t launch_append(qm_kv_pool* pool, int32_t layer, const AppendArgs& proto, 
     const long long warps = (a.rows_total + rows_per_warp - 1) / rows_per_warp;
     const long long blocks = (warps + kAppendWarps - 1) / kAppendWarps;
     if (blocks > 0x7fffffffLL) return qm_fail(QM_ECAPACITY, "too many rows for one append launch");
+    const dim3 grid((unsigned)blocks), block(kAppendWarps * 32);
     if (rows_per_warp == 4)
-        qm_norm_rope_append_kernel<4><<<(unsigned)blocks, kAppendWarps * 32, 0, stream>>>(a);
+        QM_CUDA_TRY(qm_launch(qm_norm_rope_append_kernel<4>, grid, block, 0, stream, a), "QK norm/RoPE/cache launch");
     else if (rows_per_warp == 2)
-        qm_norm_rope_append_kernel<2><<<(unsigned)blocks, kAppendWarps * 32, 0, stream>>>(a);
+        QM_CUDA_TRY(qm_launch(qm_norm_rope_append_kernel<2>, grid, block, 0, stream, a), "QK norm/RoPE/cache launch");
     else
-        qm_norm_rope_append_kernel<1><<<(unsigned)blocks, kAppendWarps * 32, 0, stream>>>(a);
+        QM_CUDA_TRY(qm_launch(qm_norm_rope_append_kernel<1>, grid, block, 0, stream, a), "QK norm/RoPE/cache launch");
     QM_CUDA_TRY(cudaGetLastError(), "QK norm/RoPE/cache launch");
     return QM_OK;
 }

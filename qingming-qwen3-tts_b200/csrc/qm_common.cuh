@@ -41,7 +41,35 @@ int32_t qm_fail_cuda(cudaError_t status, const char* operation);
         if (qm_cuda_status != cudaSuccess) return qm_fail_cuda(qm_cuda_status, what); \
     } while (0)
 
+// Launch with programmatic dependent launch allowed: the kernel may start its
+// prologue while the previous kernel on the stream drains; it must call
+// pdl_wait() before it touches global memory.  Set QM_DISABLE_PDL=1 in the
+// environment to launch with plain stream ordering instead.
+bool qm_pdl_enabled();
+
 #ifdef __CUDACC__
+
+#include <utility>
+
+template <typename... KArgs, typename... Args>
+cudaError_t qm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = qm_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+// Blocks until the kernels this launch depends on have completed and their writes are visible.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel on the stream begin launching (it still waits in its own pdl_wait()).
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- bf16 <-> f32, bit-level (same rounding as 17.cu:15082-15104)
 
@@ -65,6 +93,32 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+
+// Packed fp32 pair FMA (sm_100): d = a * b + c on both halves, one issue slot.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+
+// Packed bf16 pair -> (low, high) as floats.
+__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t pair) { return make_float2(bf16_lo(pair), bf16_hi(pair)); }
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;

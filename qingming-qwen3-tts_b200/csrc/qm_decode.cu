@@ -66,7 +66,8 @@ struct SharedLayout {
     static constexpr int kScoreOff = kPrefixOff + ((kMaxBatchPerLaunch + 1) * 4 + 15) / 16 * 16;
     static constexpr int kMergeOff = kScoreOff + 2 * 2 * kPageTokens * 4;          // float[2][2][64]
     static constexpr int kMergeLOff = kMergeOff + kConsumerWarps * 2 * kHeadDim * 4;
-    static constexpr int kMetaOff = kMergeLOff + kConsumerWarps * 2 * 4;
+    static constexpr int kQOff = kMergeLOff + kConsumerWarps * 2 * 4;              // bf16[kStages][2][128]
+    static constexpr int kMetaOff = kQOff + kStages * 2 * kHeadDim * 2;
     static constexpr int kBarOff = kMetaOff + kStages * 16;
     static constexpr int kTotal = kBarOff + 2 * kStages * 8;
 };
@@ -97,19 +98,22 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
     const int lane = tid & 31;
     const int hkv = a.kv_heads;
 
-    // Units per stream, then an inclusive scan -> prefix[s] = first unit of stream s.
-    for (int s = tid; s < a.batch; s += kDecodeThreads) {
-        const int len = clamp_len(a.seq_lens[s], a.max_pages, a.status);
-        prefix[s + 1] = ((len + kPageTokens - 1) >> 6) * hkv;
-    }
+    pdl_trigger();
     if (tid == 0) {
-        prefix[0] = 0;
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), kConsumerWarps);
         }
         fence_mbar_init();
     }
+    pdl_wait();      // everything below reads what earlier kernels on the stream wrote
+
+    // Units per stream, then an inclusive scan -> prefix[s] = first unit of stream s.
+    for (int s = tid; s < a.batch; s += kDecodeThreads) {
+        const int len = clamp_len(a.seq_lens[s], a.max_pages, a.status);
+        prefix[s + 1] = ((len + kPageTokens - 1) >> 6) * hkv;
+    }
+    if (tid == 0) prefix[0] = 0;
     __syncthreads();
     if (warp == 0) {
         int carry = 0;
@@ -181,7 +185,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                     const uint32_t bytes = (uint32_t)nvalid * kHeadDim * 2;
                     const size_t tile = ((size_t)page_id * hkv + head) * kTileElems;
                     const uint32_t dst = smem_addr(smem + stage * kStageBytes);
-                    mbar_arrive_expect_tx(full_bar(stage), 2 * bytes);
+                    const bool new_segment = n == 0 || page_idx == 0;
+                    constexpr uint32_t kQBytes = 2 * kHeadDim * 2;         // the two query heads of this KV head
+                    mbar_arrive_expect_tx(full_bar(stage), 2 * bytes + (new_segment ? kQBytes : 0u));
+                    if (new_segment)
+                        bulk_copy_g2s(smem_addr(smem + SharedLayout::kQOff + stage * kQBytes),
+                                      a.q_rot + (size_t)seg * 2 * kHeadDim, kQBytes, full_bar(stage));
                     bulk_copy_g2s(dst, a.key_pool + tile, bytes, full_bar(stage));
                     bulk_copy_g2s(dst + kTileBytes, a.value_pool + tile, bytes, full_bar(stage));
                 }
@@ -202,11 +211,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
     // --------------------------------------------------------------- consumers
     const int half = lane >> 4;
     const int lp = lane & 15;
-    float q0[8], q1[8], o0[8], o1[8];
+    float2 q0[4], q1[4], o0[4], o1[4];          // dims 8*lp .. 8*lp+7 as (even, odd) pairs
     float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.0f, l1 = 0.0f;
     bool seg_from_start = false;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) q0[j] = q1[j] = o0[j] = o1[j] = 0.0f;
+    for (int j = 0; j < 4; ++j) q0[j] = q1[j] = o0[j] = o1[j] = make_float2(0.0f, 0.0f);
 
     for (int n = 0; n < count; ++n) {
         const int stage = n % kStages;
@@ -219,20 +228,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
 
         if (n == 0 || page_idx == 0) {
             // New segment: fetch the two query heads of this KV head.
+            // The producer staged q_rot rows (2*head, 2*head+1) of this stream beside the tile.
             const float qscale = kLog2e / sqrtf((float)kHeadDim);
-            const uint16_t* qp = a.q_rot + ((size_t)stream * (2 * hkv) + 2 * head) * kHeadDim + 8 * lp;
+            const float2 qs2 = make_float2(qscale, qscale);
+            const unsigned char* qp = smem + SharedLayout::kQOff + stage * (2 * kHeadDim * 2) + lp * 16;
             const uint4 qa = *reinterpret_cast<const uint4*>(qp);
-            const uint4 qb = *reinterpret_cast<const uint4*>(qp + kHeadDim);
-            q0[0] = bf16_lo(qa.x) * qscale; q0[1] = bf16_hi(qa.x) * qscale;
-            q0[2] = bf16_lo(qa.y) * qscale; q0[3] = bf16_hi(qa.y) * qscale;
-            q0[4] = bf16_lo(qa.z) * qscale; q0[5] = bf16_hi(qa.z) * qscale;
-            q0[6] = bf16_lo(qa.w) * qscale; q0[7] = bf16_hi(qa.w) * qscale;
-            q1[0] = bf16_lo(qb.x) * qscale; q1[1] = bf16_hi(qb.x) * qscale;
-            q1[2] = bf16_lo(qb.y) * qscale; q1[3] = bf16_hi(qb.y) * qscale;
-            q1[4] = bf16_lo(qb.z) * qscale; q1[5] = bf16_hi(qb.z) * qscale;
-            q1[6] = bf16_lo(qb.w) * qscale; q1[7] = bf16_hi(qb.w) * qscale;
+            const uint4 qb = *reinterpret_cast<const uint4*>(qp + kHeadDim * 2);
+            q0[0] = fmul2(bf16x2_to_float2(qa.x), qs2); q0[1] = fmul2(bf16x2_to_float2(qa.y), qs2);
+            q0[2] = fmul2(bf16x2_to_float2(qa.z), qs2); q0[3] = fmul2(bf16x2_to_float2(qa.w), qs2);
+            q1[0] = fmul2(bf16x2_to_float2(qb.x), qs2); q1[1] = fmul2(bf16x2_to_float2(qb.y), qs2);
+            q1[2] = fmul2(bf16x2_to_float2(qb.z), qs2); q1[3] = fmul2(bf16x2_to_float2(qb.w), qs2);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o0[j] = o1[j] = 0.0f;
+            for (int j = 0; j < 4; ++j) o0[j] = o1[j] = make_float2(0.0f, 0.0f);
             m0 = m1 = -CUDART_INF_F;
             l0 = l1 = 0.0f;
             seg_from_start = page_idx == 0;
@@ -248,16 +255,16 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
         for (int i = 0; i < 4; ++i) {
             const int key = 8 * warp + 2 * i + half;
             const uint4 kk = *reinterpret_cast<const uint4*>(ktile + key * (kHeadDim * 2) + lp * 16);
-            const float kf[8] = {bf16_lo(kk.x), bf16_hi(kk.x), bf16_lo(kk.y), bf16_hi(kk.y),
-                                 bf16_lo(kk.z), bf16_hi(kk.z), bf16_lo(kk.w), bf16_hi(kk.w)};
-            float d0 = 0.0f, d1 = 0.0f;
+            const float2 kf[4] = {bf16x2_to_float2(kk.x), bf16x2_to_float2(kk.y), bf16x2_to_float2(kk.z),
+                                  bf16x2_to_float2(kk.w)};
+            float2 d0 = make_float2(0.0f, 0.0f), d1 = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                d0 = fmaf(q0[j], kf[j], d0);
-                d1 = fmaf(q1[j], kf[j], d1);
+            for (int j = 0; j < 4; ++j) {
+                d0 = ffma2(q0[j], kf[j], d0);
+                d1 = ffma2(q1[j], kf[j], d1);
             }
-            acc[2 * i] = d0;
-            acc[2 * i + 1] = d1;
+            acc[2 * i] = d0.x + d0.y;
+            acc[2 * i + 1] = d1.x + d1.y;
         }
         {
             // Reduce-scatter over the 16 lanes of a half-warp: 8 values -> lane
@@ -297,10 +304,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
         const float mn0 = fmaxf(m0, x0), mn1 = fmaxf(m1, x1);
         if (mn0 != m0 || mn1 != m1) {
             const float c0 = fast_exp2(m0 - mn0), c1 = fast_exp2(m1 - mn1);
+            const float2 c02 = make_float2(c0, c0), c12 = make_float2(c1, c1);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                o0[j] *= c0;
-                o1[j] *= c1;
+            for (int j = 0; j < 4; ++j) {
+                o0[j] = fmul2(o0[j], c02);
+                o1[j] = fmul2(o1[j], c12);
             }
             l0 *= c0;
             l1 *= c1;
@@ -318,12 +326,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                 l0 += p0;
                 l1 += p1;
                 const uint4 vv = *reinterpret_cast<const uint4*>(vtile + key * (kHeadDim * 2) + lp * 16);
-                const float vf[8] = {bf16_lo(vv.x), bf16_hi(vv.x), bf16_lo(vv.y), bf16_hi(vv.y),
-                                     bf16_lo(vv.z), bf16_hi(vv.z), bf16_lo(vv.w), bf16_hi(vv.w)};
+                const float2 vf[4] = {bf16x2_to_float2(vv.x), bf16x2_to_float2(vv.y), bf16x2_to_float2(vv.z),
+                                      bf16x2_to_float2(vv.w)};
+                const float2 p02 = make_float2(p0, p0), p12 = make_float2(p1, p1);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    o0[j] = fmaf(p0, vf[j], o0[j]);
-                    o1[j] = fmaf(p1, vf[j], o1[j]);
+                for (int j = 0; j < 4; ++j) {
+                    o0[j] = ffma2(p02, vf[j], o0[j]);
+                    o1[j] = ffma2(p12, vf[j], o1[j]);
                 }
             }
         }
@@ -333,19 +342,21 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
         // ---- end of this CTA's share of the segment
         if (n == count - 1 || page_idx == pages - 1) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                o0[j] += __shfl_xor_sync(0xffffffffu, o0[j], 16);
-                o1[j] += __shfl_xor_sync(0xffffffffu, o1[j], 16);
+            for (int j = 0; j < 4; ++j) {
+                o0[j].x += __shfl_xor_sync(0xffffffffu, o0[j].x, 16);
+                o0[j].y += __shfl_xor_sync(0xffffffffu, o0[j].y, 16);
+                o1[j].x += __shfl_xor_sync(0xffffffffu, o1[j].x, 16);
+                o1[j].y += __shfl_xor_sync(0xffffffffu, o1[j].y, 16);
             }
             l0 += __shfl_xor_sync(0xffffffffu, l0, 16);
             l1 += __shfl_xor_sync(0xffffffffu, l1, 16);
             if (half == 0) {
                 float* dst0 = merge_o + (warp * 2 + 0) * kHeadDim + 8 * lp;
                 float* dst1 = merge_o + (warp * 2 + 1) * kHeadDim + 8 * lp;
-                *reinterpret_cast<float4*>(dst0) = make_float4(o0[0], o0[1], o0[2], o0[3]);
-                *reinterpret_cast<float4*>(dst0 + 4) = make_float4(o0[4], o0[5], o0[6], o0[7]);
-                *reinterpret_cast<float4*>(dst1) = make_float4(o1[0], o1[1], o1[2], o1[3]);
-                *reinterpret_cast<float4*>(dst1 + 4) = make_float4(o1[4], o1[5], o1[6], o1[7]);
+                *reinterpret_cast<float4*>(dst0) = make_float4(o0[0].x, o0[0].y, o0[1].x, o0[1].y);
+                *reinterpret_cast<float4*>(dst0 + 4) = make_float4(o0[2].x, o0[2].y, o0[3].x, o0[3].y);
+                *reinterpret_cast<float4*>(dst1) = make_float4(o1[0].x, o1[0].y, o1[1].x, o1[1].y);
+                *reinterpret_cast<float4*>(dst1 + 4) = make_float4(o1[2].x, o1[2].y, o1[3].x, o1[3].y);
             }
             if (lane == 0) {
                 merge_l[warp * 2 + 0] = l0;
@@ -387,6 +398,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
 
 // Folds the per-CTA partials of one (stream, kv head) segment, in CTA order.
 __global__ void __launch_bounds__(256) qm_decode_combine_kernel(const DecodeArgs a, int grid_main) {
+    pdl_trigger();
+    pdl_wait();
     const int seg = blockIdx.x;
     const int hkv = a.kv_heads;
     const int stream = seg / hkv;
@@ -439,6 +452,8 @@ __global__ void __launch_bounds__(256) qm_decode_combine_kernel(const DecodeArgs
 // partials [parts][rows][130] (m in natural-log domain) -> out [rows][128] bf16.
 __global__ void __launch_bounds__(128) qm_combine_partials_kernel(const float* __restrict__ partials, int parts,
                                                                   int rows, uint16_t* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     const int d = threadIdx.x;
     float big = -CUDART_INF_F;
@@ -504,10 +519,10 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
         a.out = out ? out + (size_t)begin * q_heads * kHeadDim : nullptr;
         a.partial_out = partial_out ? partial_out + (size_t)begin * q_heads * kPartialStride : nullptr;
         a.batch = n;
-        qm_decode_splitkv_kernel<<<grid, kDecodeThreads, SharedLayout::kTotal, stream>>>(a);
-        QM_CUDA_TRY(cudaGetLastError(), "split-KV decode attention launch");
-        qm_decode_combine_kernel<<<n * pool->kv_heads, 256, 0, stream>>>(a, grid);
-        QM_CUDA_TRY(cudaGetLastError(), "decode attention combine launch");
+        QM_CUDA_TRY(qm_launch(qm_decode_splitkv_kernel, dim3(grid), dim3(kDecodeThreads), SharedLayout::kTotal, stream, a),
+                    "split-KV decode attention launch");
+        QM_CUDA_TRY(qm_launch(qm_decode_combine_kernel, dim3(n * pool->kv_heads), dim3(256), 0, stream, a, grid),
+                    "decode attention combine launch");
     }
     return QM_OK;
 }
@@ -541,8 +556,9 @@ int32_t qm_attention_combine(const float* partials, int32_t parts, int32_t rows,
     if (!partials || !out) return qm_fail(QM_EINVAL, "null tensor pointer");
     if (parts < 1 || rows < 0) return qm_fail(QM_EINVAL, "parts must be >= 1 and rows >= 0");
     if (rows == 0) return QM_OK;
-    qm_combine_partials_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(partials, parts, rows, out);
-    QM_CUDA_TRY(cudaGetLastError(), "attention combine launch");
+    QM_CUDA_TRY(qm_launch(qm_combine_partials_kernel, dim3(rows), dim3(128), 0, static_cast<cudaStream_t>(stream), partials,
+                          (int)parts, (int)rows, out),
+                "attention combine launch");
     return QM_OK;
 }
 

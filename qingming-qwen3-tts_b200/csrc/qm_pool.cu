@@ -2,6 +2,7 @@
 // gate, the paged KV pool object and the RoPE table.
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -21,6 +22,14 @@ int32_t qm_fail_cuda(cudaError_t status, const char* operation) {
     std::snprintf(g_error_text, sizeof(g_error_text), "%s: %s", operation, cudaGetErrorString(status));
     if (status == cudaErrorMemoryAllocation) return QM_ENOMEM;
     return QM_ECUDA;
+}
+
+bool qm_pdl_enabled() {
+    static const bool enabled = [] {
+        const char* v = std::getenv("QM_DISABLE_PDL");
+        return !(v && v[0] == '1');
+    }();
+    return enabled;
 }
 
 // Defined in qm_prefill.cu: builds the per-layer tiled tensor maps.

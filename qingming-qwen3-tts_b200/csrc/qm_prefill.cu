@@ -167,6 +167,8 @@ __host__ __device__ constexpr uint32_t instr_desc(bool b_mn_major) {
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 qm_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                             const __grid_constant__ CUtensorMap v_map, const PrefillArgs a) {
+    pdl_trigger();
+    pdl_wait();
     // ---- which work item: heaviest query blocks first
     const int per_block_row = a.batch * a.kv_heads;
     const int qblock = a.max_qblocks - 1 - (int)(blockIdx.x / per_block_row);
@@ -534,8 +536,8 @@ extern "C" int32_t qm_prefill_attention_varlen(qm_kv_pool* pool, int32_t layer, 
     a.max_qblocks = (max_seqlen + kBlockM - 1) / kBlockM;
     const long long blocks = (long long)a.max_qblocks * batch * pool->kv_heads;
     if (blocks > 0x7fffffffLL) return qm_fail(QM_ECAPACITY, "too many query blocks for one launch");
-    qm_prefill_attention_kernel<<<(unsigned)blocks, kPrefillThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(
-        q_map, pool->key_maps[layer], pool->value_maps[layer], a);
-    QM_CUDA_TRY(cudaGetLastError(), "Talker prefill attention launch");
+    QM_CUDA_TRY(qm_launch(qm_prefill_attention_kernel, dim3((unsigned)blocks), dim3(kPrefillThreads), (size_t)smem_bytes,
+                          static_cast<cudaStream_t>(stream), q_map, pool->key_maps[layer], pool->value_maps[layer], a),
+                "Talker prefill attention launch");
     return QM_OK;
 }
