@@ -144,6 +144,13 @@ int32_t qm_prefill_append_rope_varlen(qm_kv_pool* pool, int32_t layer, const uin
 /* Bytes of caller-owned scratch qm_decode_attention needs for a batch. */
 int64_t qm_decode_workspace_bytes(int32_t batch, int32_t kv_heads);
 
+/* Zero-fills a freshly allocated workspace on `stream` (the reference clears
+ * its buffers the same way when it creates them, 17.cu:16419-16438).  Call it
+ * once after allocating: the per-segment arrival counters inside must start
+ * at zero; every call leaves them at zero again.  Call it again after a call
+ * that reported QM_DEVSTAT_TIMEOUT. */
+int32_t qm_decode_workspace_init(void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Split-KV flash decoding over the paged cache, q_heads == 2 * kv_heads.
  *   q_rot [batch][q_heads][128]: output of qm_decode_append_rope
  *   seq_lens[batch]: number of keys each stream attends, i.e. position + 1
@@ -151,7 +158,10 @@ int64_t qm_decode_workspace_bytes(int32_t batch, int32_t kv_heads);
  *   out [batch][q_heads][128] bf16, the reference's `context`
  * Softmax scale is 1/sqrtf(128) (17.cu:17910-17914).  Scores, softmax and the
  * PV sum stay in fp32; the result is rounded to bf16 once.  Deterministic:
- * the split of keys over CTAs depends only on seq_lens and the SM count. */
+ * the split of keys over CTAs depends only on seq_lens and the SM count, and
+ * partial results are always folded in the same order.  `workspace` must have
+ * been prepared once with qm_decode_workspace_init and must not be shared by
+ * calls that overlap on the GPU. */
 int32_t qm_decode_attention(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const int32_t* seq_lens,
                             const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads,
                             uint16_t* out, void* workspace, int64_t workspace_bytes, void* stream);
@@ -170,7 +180,8 @@ int32_t qm_decode_attention(qm_kv_pool* pool, int32_t layer, const uint16_t* q_r
  *     pool's device must be current); make that first call before starting
  *     any stream capture.
  *   - all calls on a device share the one array and it keeps what the last
- *     call wrote; nothing in it needs clearing between calls, but two calls
+ *     call wrote; it starts zeroed and the kernel re-zeroes the counters it
+ *     uses, so nothing needs clearing between calls, but two calls
  *     whose kernels overlap on the GPU (different streams, or several
  *     threads) would overwrite each other's partials: issue them on one
  *     stream, or order them with events.

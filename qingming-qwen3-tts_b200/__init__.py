@@ -63,6 +63,7 @@ ABI = {
                                       [c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                        c_float, c_void_p, c_void_p]),
     "qm_decode_workspace_bytes": (c_int64, [c_int32, c_int32]),
+    "qm_decode_workspace_init": (c_int32, [c_void_p, c_int64, c_void_p]),
     "qm_decode_attention": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                       c_void_p, c_void_p, c_int64, c_void_p]),
     "qm_decode_attention_static": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
@@ -226,6 +227,7 @@ class TalkerAttention:
         need = self.lib.qm_decode_workspace_bytes(batch, self.kv_heads)
         if self._workspace is None or self._workspace.numel() < need:
             self._workspace = torch.empty(need, dtype=torch.uint8, device="cuda")
+            _check(self.lib.qm_decode_workspace_init(_ptr(self._workspace), need, _stream()))
         return self._workspace
 
     def launch_attention(self, layer, q_rot, seq_lens, page_table, out=None):

@@ -18,8 +18,10 @@
 //   * writes a segment's result directly when one CTA saw all of it, else an
 //     (m, l, o) partial into slot (cta + segment) of the workspace - that map
 //     is injective over the (cta, segment) pairs that occur because both
-//     indices only grow along the unit order - and a second kernel folds the
-//     partials in CTA order, so results do not depend on timing.
+//     indices only grow along the unit order.  Each CTA then bumps the
+//     segment's arrival counter; the CTA that arrives last folds all partials
+//     of the segment in CTA order (so the result does not depend on which CTA
+//     that is) and sets the counter back to zero for the next call.
 //
 // Scores live in the log2 domain (q is pre-multiplied by scale * log2 e).
 #include <math_constants.h>
@@ -50,8 +52,7 @@ struct DecodeArgs {
     uint16_t* out;           // mode 0
     float* partial_out;      // mode 1: [batch][q_heads][130]
     float* ws_partials;      // [(grid + segments)][2][130]
-    int32_t* ws_first;       // [segments] first CTA that holds part of the segment
-    int32_t* ws_last;        // [segments] last CTA
+    int32_t* ws_count;       // [segments] arrival counters, zero between calls
     uint32_t* status;
     int batch;
     int kv_heads;
@@ -69,7 +70,8 @@ struct SharedLayout {
     static constexpr int kQOff = kMergeLOff + kConsumerWarps * 2 * 4;              // bf16[kStages][2][128]
     static constexpr int kMetaOff = kQOff + kStages * 2 * kHeadDim * 2;
     static constexpr int kBarOff = kMetaOff + kStages * 16;
-    static constexpr int kTotal = kBarOff + 2 * kStages * 8;
+    static constexpr int kFlagOff = kBarOff + 2 * kStages * 8;
+    static constexpr int kTotal = kFlagOff + 16;
 };
 
 __device__ __forceinline__ int clamp_len(int len, int max_pages, uint32_t* status) {
@@ -89,6 +91,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
     float* merge_o = reinterpret_cast<float*>(smem + SharedLayout::kMergeOff);
     float* merge_l = reinterpret_cast<float*>(smem + SharedLayout::kMergeLOff);
     int4* meta = reinterpret_cast<int4*>(smem + SharedLayout::kMetaOff);
+    volatile int* fold_flag = reinterpret_cast<volatile int*>(smem + SharedLayout::kFlagOff);
     const uint32_t bar_base = smem_addr(smem + SharedLayout::kBarOff);
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
@@ -131,6 +134,25 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
         }
     }
     __syncthreads();
+
+    // Streams with nothing to attend get a zero row (mode 0) or an empty partial (mode 1).
+    for (int s = blockIdx.x; s < a.batch; s += gridDim.x) {
+        if (prefix[s + 1] != prefix[s]) continue;
+        for (int i = tid; i < 2 * hkv * kHeadDim; i += kDecodeThreads) {
+            const size_t row = (size_t)s * (2 * hkv) + i / kHeadDim;
+            const int d = i % kHeadDim;
+            if (a.mode == 0) {
+                a.out[row * kHeadDim + d] = 0;
+            } else {
+                float* dst = a.partial_out + row * kPartialStride;
+                dst[2 + d] = 0.0f;
+                if (d == 0) {
+                    dst[0] = -CUDART_INF_F;
+                    dst[1] = 0.0f;
+                }
+            }
+        }
+    }
 
     const long long total_units = prefix[a.batch];
     const long long grid_eff = total_units < (long long)gridDim.x ? total_units : (long long)gridDim.x;
@@ -375,76 +397,63 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                 const float m = qh ? m1 : m0;
                 const bool whole = seg_from_start && page_idx == pages - 1;
                 const size_t row = (size_t)stream * (2 * hkv) + 2 * head + qh;
-                if (whole && a.mode == 0) {
-                    a.out[row * kHeadDim + d] = (uint16_t)f32_to_bf16_bits(sum / lsum);
+                if (whole) {
+                    if (a.mode == 0) {
+                        a.out[row * kHeadDim + d] = (uint16_t)f32_to_bf16_bits(sum / lsum);
+                    } else {
+                        float* dst = a.partial_out + row * kPartialStride;
+                        dst[2 + d] = sum;
+                        if (d == 0) {
+                            dst[0] = m * kLn2;
+                            dst[1] = lsum;
+                        }
+                    }
                 } else {
-                    float* dst = whole ? a.partial_out + row * kPartialStride
-                                       : a.ws_partials + ((size_t)(cta + seg) * 2 + qh) * kPartialStride;
+                    float* dst = a.ws_partials + ((size_t)(cta + seg) * 2 + qh) * kPartialStride;
                     dst[2 + d] = sum;
                     if (d == 0) {
-                        dst[0] = whole ? m * kLn2 : m;
+                        dst[0] = m;
                         dst[1] = lsum;
                     }
-                }
-                if (tid == 0) {
-                    if (seg_from_start) a.ws_first[seg] = cta;
-                    if (page_idx == pages - 1) a.ws_last[seg] = cta;
+                    // Which CTAs hold a part of this segment (unit u belongs to CTA ((u + 1) * G - 1) / U).
+                    const long long u_first = (long long)prefix[stream] + (long long)head * pages;
+                    const int c_first = (int)(((u_first + 1) * grid_eff - 1) / total_units);
+                    const int c_last = (int)(((u_first + pages) * grid_eff - 1) / total_units);
+                    __threadfence();
+                    named_bar_sync(1, kConsumerThreads);
+                    if (tid == 0) {
+                        const int arrived = atomicAdd(a.ws_count + seg, 1) + 1;
+                        const int is_last = arrived == c_last - c_first + 1;
+                        if (is_last) a.ws_count[seg] = 0;          // everyone else is done with it
+                        *fold_flag = is_last;
+                    }
+                    named_bar_sync(1, kConsumerThreads);
+                    if (*fold_flag) {
+                        __threadfence();
+                        float big = -CUDART_INF_F;
+                        for (int c = c_first; c <= c_last; ++c)
+                            big = fmaxf(big, __ldcg(a.ws_partials + ((size_t)(c + seg) * 2 + qh) * kPartialStride));
+                        float acc = 0.0f, denom = 0.0f;
+                        for (int c = c_first; c <= c_last; ++c) {
+                            const float* src = a.ws_partials + ((size_t)(c + seg) * 2 + qh) * kPartialStride;
+                            const float w = fast_exp2(__ldcg(src) - big);
+                            denom = fmaf(w, __ldcg(src + 1), denom);
+                            acc = fmaf(w, __ldcg(src + 2 + d), acc);
+                        }
+                        if (a.mode == 0) {
+                            a.out[row * kHeadDim + d] = (uint16_t)f32_to_bf16_bits(acc / denom);
+                        } else {
+                            float* out_partial = a.partial_out + row * kPartialStride;
+                            out_partial[2 + d] = acc;
+                            if (d == 0) {
+                                out_partial[0] = big * kLn2;
+                                out_partial[1] = denom;
+                            }
+                        }
+                    }
                 }
             }
             named_bar_sync(1, kConsumerThreads);
-        }
-    }
-}
-
-// Folds the per-CTA partials of one (stream, kv head) segment, in CTA order.
-__global__ void __launch_bounds__(256) qm_decode_combine_kernel(const DecodeArgs a, int grid_main) {
-    pdl_trigger();
-    pdl_wait();
-    const int seg = blockIdx.x;
-    const int hkv = a.kv_heads;
-    const int stream = seg / hkv;
-    const int head = seg - stream * hkv;
-    const int qh = threadIdx.x >> 7;
-    const int d = threadIdx.x & 127;
-    const size_t row = (size_t)stream * (2 * hkv) + 2 * head + qh;
-    const int len = a.seq_lens[stream];
-    if (len <= 0) {
-        if (a.mode == 0) {
-            a.out[row * kHeadDim + d] = 0;
-        } else {
-            float* dst = a.partial_out + row * kPartialStride;
-            dst[2 + d] = 0.0f;
-            if (d == 0) {
-                dst[0] = -CUDART_INF_F;
-                dst[1] = 0.0f;
-            }
-        }
-        return;
-    }
-    const int first = a.ws_first[seg], last = a.ws_last[seg];
-    if (first == last) return;       // the main kernel wrote this segment itself
-    if (first < 0 || last >= grid_main || last < first) {
-        if (threadIdx.x == 0) atomicOr(a.status, QM_DEVSTAT_BAD_PAGE);
-        return;
-    }
-    float big = -CUDART_INF_F;
-    for (int c = first; c <= last; ++c)
-        big = fmaxf(big, a.ws_partials[((size_t)(c + seg) * 2 + qh) * kPartialStride]);
-    float acc = 0.0f, denom = 0.0f;
-    for (int c = first; c <= last; ++c) {
-        const float* src = a.ws_partials + ((size_t)(c + seg) * 2 + qh) * kPartialStride;
-        const float w = fast_exp2(src[0] - big);
-        denom = fmaf(w, src[1], denom);
-        acc = fmaf(w, src[2 + d], acc);
-    }
-    if (a.mode == 0) {
-        a.out[row * kHeadDim + d] = (uint16_t)f32_to_bf16_bits(acc / denom);
-    } else {
-        float* dst = a.partial_out + row * kPartialStride;
-        dst[2 + d] = acc;
-        if (d == 0) {
-            dst[0] = big * kLn2;
-            dst[1] = denom;
         }
     }
 }
@@ -504,8 +513,7 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
     a.key_pool = qm_kv_pool_key_ptr(pool, layer);
     a.value_pool = qm_kv_pool_value_ptr(pool, layer);
     a.ws_partials = reinterpret_cast<float*>(ws);
-    a.ws_first = reinterpret_cast<int32_t*>(ws + partials_bytes(segs_cap));
-    a.ws_last = a.ws_first + segs_cap;
+    a.ws_count = reinterpret_cast<int32_t*>(ws + partials_bytes(segs_cap));
     a.status = pool->status_dev;
     a.kv_heads = pool->kv_heads;
     a.max_pages = max_pages;
@@ -521,8 +529,6 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
         a.batch = n;
         QM_CUDA_TRY(qm_launch(qm_decode_splitkv_kernel, dim3(grid), dim3(kDecodeThreads), SharedLayout::kTotal, stream, a),
                     "split-KV decode attention launch");
-        QM_CUDA_TRY(qm_launch(qm_decode_combine_kernel, dim3(n * pool->kv_heads), dim3(256), 0, stream, a, grid),
-                    "decode attention combine launch");
     }
     return QM_OK;
 }
@@ -535,6 +541,13 @@ int64_t qm_decode_workspace_bytes(int32_t batch, int32_t kv_heads) {
     if (batch < 0 || kv_heads < 1) return 0;
     const int segs = (batch < kMaxBatchPerLaunch ? batch : kMaxBatchPerLaunch) * kv_heads;
     return (int64_t)partials_bytes(segs) + (int64_t)segs * 2 * sizeof(int32_t) + 256;
+}
+
+int32_t qm_decode_workspace_init(void* workspace, int64_t workspace_bytes, void* stream) {
+    if (!workspace || workspace_bytes <= 0) return qm_fail(QM_EINVAL, "workspace is null or empty");
+    QM_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)workspace_bytes, static_cast<cudaStream_t>(stream)),
+                "clear decode workspace");
+    return QM_OK;
 }
 
 int32_t qm_decode_attention(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const int32_t* seq_lens,
@@ -580,7 +593,7 @@ constexpr int kStaticMaxBatch = 64;
 constexpr int kStaticMaxKvHeads = 8;
 constexpr size_t kStaticScratchBytes =
     (size_t)(kMaxGrid + kStaticMaxBatch * kStaticMaxKvHeads) * 2 * kPartialStride * sizeof(float)   // partials
-    + (size_t)kStaticMaxBatch * kStaticMaxKvHeads * 2 * sizeof(int32_t)                             // first / last CTA
+    + (size_t)kStaticMaxBatch * kStaticMaxKvHeads * 2 * sizeof(int32_t)                             // arrival counters
     + 256;
 
 static __device__ __align__(256) unsigned char qm_static_decode_scratch[kStaticScratchBytes];
@@ -626,9 +639,11 @@ extern "C" int32_t qm_decode_attention_static(qm_kv_pool* pool, int32_t layer, c
     void* scratch = nullptr;
     const int32_t looked_up = static_scratch_address(pool->device, &scratch);
     if (looked_up != QM_OK) return looked_up;
-    // Nothing in the scratch has to start at zero: every partial slot and every
-    // first/last entry that the combine step reads is written earlier in the
-    // same call, so what the previous call left behind is never consumed.
+    // The only part of the scratch that must start at zero is the per-segment
+    // arrival counters.  The array is zero when the library is loaded, and the
+    // kernel puts every counter it used back to zero before it finishes, so no
+    // clearing is needed here; partial slots are always written before they are
+    // read within one call, so leftovers from the previous call are never used.
     return run_decode(pool, layer, q_rot, seq_lens, page_table, max_pages, batch, q_heads, out, nullptr, scratch,
                       (int64_t)kStaticScratchBytes, static_cast<cudaStream_t>(stream), 0);
 }
