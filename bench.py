@@ -398,11 +398,11 @@ def prefill_lengths():
     return splitmix64_ints(2 * 1000 + 99, 1024, 8192, 8)
 
 
-def run_prefill_section(pkg, steps, warmup):
+def run_prefill_section(pkg, steps, warmup, n_seqs=8):
     """Secondary measurement: varlen causal prefill (fused append + tcgen05 attention), 1.7B talker shape."""
     import torch
 
-    lengths = prefill_lengths()
+    lengths = prefill_lengths()[:n_seqs]
     cu = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
     total = int(cu[-1])
     pages_per_seq = (lengths + PAGE - 1) // PAGE
@@ -565,11 +565,23 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the secondary prefill measurement")
+    ap.add_argument("--only-prefill", action="store_true", help="run only the prefill section (profiling aid)")
+    ap.add_argument("--prefill-seqs", type=int, default=8, help="with --only-prefill: use the first N prompts")
     ap.add_argument("--no-long-context", action="store_true", help="skip the secondary split-KV long-context measurement")
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="layers per step (default: the talker's 28); a smaller value gives a small case for profiling")
     args = ap.parse_args()
     LAYERS = args.layers
+    if args.only_prefill:
+        import torch
+
+        import __graft_entry__ as entry
+
+        torch.cuda.set_device(0)
+        pkg = entry.load_package()
+        pkg.load_library()
+        print(json.dumps(run_prefill_section(pkg, args.steps, args.warmup, args.prefill_seqs)))
+        return
     if args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -117,6 +117,17 @@ __device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
     return d;
 }
 
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+
 // Packed bf16 pair -> (low, high) as floats.
 __device__ __forceinline__ float2 bf16x2_to_float2(uint32_t pair) { return make_float2(bf16_lo(pair), bf16_hi(pair)); }
 

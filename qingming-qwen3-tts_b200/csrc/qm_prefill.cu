@@ -11,8 +11,9 @@
 // are visited):
 //
 //   S_t = Q_t K_j^T      tcgen05.mma  A, B from shared memory (128B swizzle), D in TMEM
-//   P_t = softmax step   4 warps per tile, thread = row: tcgen05.ld S, fp32 max /
-//                        exp2 / sum, bf16 P written back over S with tcgen05.st
+//   P_t = softmax step   4 warps per tile, thread = row: two passes of tcgen05.ld over S
+//                        (row max, then exp2 / sum in packed fp32x2), bf16 P written back
+//                        over S with tcgen05.st
 //   O_t += P_t V_j       tcgen05.mma  A = P from TMEM, B = V tile (MN-major)
 //
 // Warp roles: warps 0-3 softmax of tile 0, warps 4-7 softmax of tile 1, warp 8
@@ -127,6 +128,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
           "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
           "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -336,24 +344,33 @@ qm_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         for (int j = 0; j < n_tiles; ++j) {
             if (!mbar_wait_bounded(bar(BAR_SFULL + t), j & 1, dead) && lane == 0) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
             tc_fence_after();
-            uint32_t sreg[4][32];
-#pragma unroll
-            for (int cch = 0; cch < 4; ++cch) tmem_ld32(s_addr + cch * 32, sreg[cch]);
-            tmem_wait_ld();
-
             const int key0 = j * kBlockN;
-            if (key0 + kBlockN - 1 > start + q0) {       // tile touches the diagonal
+            const bool diagonal = key0 + kBlockN - 1 > start + q0;       // some key of the tile lies past some row
+            const int keys_visible = qpos - key0 + 1;                    // columns [0, keys_visible) of this row count
+
+            // ---- pass 1: row maximum, 32 columns at a time (the next chunk is in flight while one is reduced)
+            uint32_t buf[2][32];
+            float mxa[8];
 #pragma unroll
-                for (int cch = 0; cch < 4; ++cch)
+            for (int i = 0; i < 8; ++i) mxa[i] = -CUDART_INF_F;
+            tmem_ld32(s_addr, buf[0]);
+#pragma unroll
+            for (int cch = 0; cch < 4; ++cch) {
+                tmem_wait_ld();
+                if (cch < 3) tmem_ld32(s_addr + (cch + 1) * 32, buf[(cch + 1) & 1]);
+                if (diagonal) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (key0 + cch * 32 + i > qpos) sreg[cch][i] = __float_as_uint(-CUDART_INF_F);
+                        if (cch * 32 + i >= keys_visible) buf[cch & 1][i] = __float_as_uint(-CUDART_INF_F);
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mxa[i & 7] = fmaxf(mxa[i & 7], __uint_as_float(buf[cch & 1][i]));
             }
-            float mx = -CUDART_INF_F;
-#pragma unroll
-            for (int cch = 0; cch < 4; ++cch)
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sreg[cch][i]));
+            const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
+                                   fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
+            // start pass 2's first load now; it completes while the maximum is settled
+            tmem_ld32(s_addr, buf[0]);
+
             const float m_new = fmaxf(m_used, mx * c);
             const bool grow = m_new - m_used > kRescaleThreshold;     // also true on the first tile (m_used = -inf)
             if (j == 0) {
@@ -366,33 +383,44 @@ qm_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 const float factor = grow ? fast_exp2(m_used - m_new) : 1.0f;
                 if (grow) m_used = m_new;
                 l *= factor;
+                tmem_wait_ld();                       // buf[0] of pass 2 has landed; keep it, use buf[1] here
 #pragma unroll
                 for (int cch = 0; cch < 4; ++cch) {
-                    uint32_t oreg[32];
-                    tmem_ld32(o_addr + cch * 32, oreg);
+                    tmem_ld32(o_addr + cch * 32, buf[1]);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * factor);
-                    tmem_st32(o_addr + cch * 32, oreg);
+                    for (int i = 0; i < 32; ++i) buf[1][i] = __float_as_uint(__uint_as_float(buf[1][i]) * factor);
+                    tmem_st32(o_addr + cch * 32, buf[1]);
                 }
                 tmem_wait_st();
             }
-            // P = exp2(s * c - m), bf16, written over the first 64 columns of S
-            float sum = 0.0f;
+
+            // ---- pass 2: P = exp2(s * c - m) as bf16 pairs, written over the first 64 columns of S.
+            // Chunk k of S (columns 32k..32k+31) becomes columns 16k..16k+15 of P, which only covers S
+            // columns that have already been read.
+            float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            const float2 c2 = make_float2(c, c), negm2 = make_float2(-m_used, -m_used);
 #pragma unroll
-            for (int cch = 0; cch < 2; ++cch) {
-                uint32_t preg[32];
+            for (int cch = 0; cch < 4; ++cch) {
+                tmem_wait_ld();
+                if (cch < 3) tmem_ld32(s_addr + (cch + 1) * 32, buf[(cch + 1) & 1]);
+                if (diagonal) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int col = cch * 64 + 2 * i;
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sreg[col >> 5][col & 31]), c, -m_used));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sreg[(col + 1) >> 5][(col + 1) & 31]), c, -m_used));
-                    sum += p0 + p1;
-                    preg[i] = pack_bf16x2(p0, p1);
+                    for (int i = 0; i < 32; ++i)
+                        if (cch * 32 + i >= keys_visible) buf[cch & 1][i] = __float_as_uint(-CUDART_INF_F);
                 }
-                tmem_st32(s_addr + cch * 32, preg);
+                uint32_t preg[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float2 x = ffma2(make_float2(__uint_as_float(buf[cch & 1][2 * i]),
+                                                       __uint_as_float(buf[cch & 1][2 * i + 1])), c2, negm2);
+                    const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                    sum2[i & 3] = fadd2(sum2[i & 3], p);
+                    preg[i] = pack_bf16x2(p.x, p.y);
+                }
+                tmem_st16(s_addr + cch * 16, preg);
             }
-            l += sum;
+            l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y) + (sum2[2].x + sum2[2].y) + (sum2[3].x + sum2[3].y);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(BAR_PREADY + t));
