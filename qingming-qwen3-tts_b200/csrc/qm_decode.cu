@@ -62,7 +62,6 @@ struct DecodeArgs {
 };
 
 struct SharedLayout {
-    static constexpr int kStagesOff = 0;
     static constexpr int kPrefixOff = kStages * kStageBytes;                       // int32[kMaxBatch+1]
     static constexpr int kScoreOff = kPrefixOff + ((kMaxBatchPerLaunch + 1) * 4 + 15) / 16 * 16;
     static constexpr int kMergeOff = kScoreOff + 2 * 2 * kPageTokens * 4;          // float[2][2][64]

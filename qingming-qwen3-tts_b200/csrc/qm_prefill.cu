@@ -39,7 +39,6 @@ namespace {
 
 constexpr int kBlockM = 128;            // query positions per CTA
 constexpr int kBlockN = 128;            // keys per tile (two pages)
-constexpr int kSoftmaxThreads = 256;
 constexpr int kPrefillThreads = 320;
 constexpr int kMmaWarp = 8;
 constexpr int kLoadWarp = 9;
@@ -130,6 +129,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -150,6 +157,34 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
+
+// 2^x for a pair on the FMA pipe instead of the special-function unit (which, at 16 results per clock per SM,
+// would otherwise bound the softmax): round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a degree-3
+// minimax polynomial for 2^f on [-0.5, 0.5] (max relative error 7.5e-5, far below a bf16 ulp), then n is added
+// into the exponent field.  x is clamped at -125 so that the biased exponent stays positive (2^-125 is 0 in bf16).
+__device__ __forceinline__ float2 exp2_poly_pair(float2 x) {
+    const float2 magic = make_float2(12582912.0f, 12582912.0f);
+    const float2 neg_magic = make_float2(-12582912.0f, -12582912.0f);
+    const float2 minus_one = make_float2(-1.0f, -1.0f);
+    x.x = fmaxf(x.x, -125.0f);
+    x.y = fmaxf(x.y, -125.0f);
+    const float2 t = fadd2(x, magic);
+    const float2 n = fadd2(t, neg_magic);
+    const float2 f = ffma2(n, minus_one, x);
+    float2 p = ffma2(f, make_float2(0.0551716685f, 0.0551716685f), make_float2(0.2426111251f, 0.2426111251f));
+    p = ffma2(p, f, make_float2(0.6932609677f, 0.6932609677f));
+    p = ffma2(p, f, make_float2(0.9999280572f, 0.9999280572f));
+    float2 r;
+    r.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23));
+    r.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23));
+    return r;
+}
+
+// Of every 8 column pairs, this many take the polynomial path; the rest use ex2.approx.
+#ifndef QM_POLY_PAIRS_OF_8
+#define QM_POLY_PAIRS_OF_8 0
+#endif
+constexpr int kPolyPairsOf8 = QM_POLY_PAIRS_OF_8;
 
 // Shared-memory matrix descriptor, 128-byte swizzle.  lbo / sbo in bytes.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -348,28 +383,28 @@ qm_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             const bool diagonal = key0 + kBlockN - 1 > start + q0;       // some key of the tile lies past some row
             const int keys_visible = qpos - key0 + 1;                    // columns [0, keys_visible) of this row count
 
-            // ---- pass 1: row maximum, 32 columns at a time (the next chunk is in flight while one is reduced)
-            uint32_t buf[2][32];
+            // ---- the whole 128-column row of S into registers (one TMEM read)
+            uint32_t sreg[4][32];
+#pragma unroll
+            for (int cch = 0; cch < 4; ++cch) tmem_ld32(s_addr + cch * 32, sreg[cch]);
+            tmem_wait_ld();
+            if (diagonal) {
+#pragma unroll
+                for (int cch = 0; cch < 4; ++cch)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (cch * 32 + i >= keys_visible) sreg[cch][i] = __float_as_uint(-CUDART_INF_F);
+            }
+            // ---- row maximum: 8 independent chains of 3-input max
             float mxa[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) mxa[i] = -CUDART_INF_F;
-            tmem_ld32(s_addr, buf[0]);
 #pragma unroll
-            for (int cch = 0; cch < 4; ++cch) {
-                tmem_wait_ld();
-                if (cch < 3) tmem_ld32(s_addr + (cch + 1) * 32, buf[(cch + 1) & 1]);
-                if (diagonal) {
+            for (int cch = 0; cch < 4; ++cch)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (cch * 32 + i >= keys_visible) buf[cch & 1][i] = __float_as_uint(-CUDART_INF_F);
-                }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mxa[i & 7] = fmaxf(mxa[i & 7], __uint_as_float(buf[cch & 1][i]));
-            }
-            const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
-                                   fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
-            // start pass 2's first load now; it completes while the maximum is settled
-            tmem_ld32(s_addr, buf[0]);
+                for (int i = 0; i < 32; i += 2)
+                    mxa[(i >> 1) & 7] = fmax3(mxa[(i >> 1) & 7], __uint_as_float(sreg[cch][i]), __uint_as_float(sreg[cch][i + 1]));
+            const float mx = fmax3(fmax3(mxa[0], mxa[1], mxa[2]), fmax3(mxa[3], mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7]));
 
             const float m_new = fmaxf(m_used, mx * c);
             const bool grow = m_new - m_used > kRescaleThreshold;     // also true on the first tile (m_used = -inf)
@@ -383,38 +418,29 @@ qm_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 const float factor = grow ? fast_exp2(m_used - m_new) : 1.0f;
                 if (grow) m_used = m_new;
                 l *= factor;
-                tmem_wait_ld();                       // buf[0] of pass 2 has landed; keep it, use buf[1] here
-#pragma unroll
-                for (int cch = 0; cch < 4; ++cch) {
-                    tmem_ld32(o_addr + cch * 32, buf[1]);
+#pragma unroll 1
+                for (int cch = 0; cch < 8; ++cch) {
+                    uint32_t oreg[16];
+                    tmem_ld16(o_addr + cch * 16, oreg);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) buf[1][i] = __float_as_uint(__uint_as_float(buf[1][i]) * factor);
-                    tmem_st32(o_addr + cch * 32, buf[1]);
+                    for (int i = 0; i < 16; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * factor);
+                    tmem_st16(o_addr + cch * 16, oreg);
                 }
                 tmem_wait_st();
             }
 
-            // ---- pass 2: P = exp2(s * c - m) as bf16 pairs, written over the first 64 columns of S.
-            // Chunk k of S (columns 32k..32k+31) becomes columns 16k..16k+15 of P, which only covers S
-            // columns that have already been read.
+            // ---- P = exp2(s * c - m) as bf16 pairs, written over the first 64 columns of S
             float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
             const float2 c2 = make_float2(c, c), negm2 = make_float2(-m_used, -m_used);
 #pragma unroll
             for (int cch = 0; cch < 4; ++cch) {
-                tmem_wait_ld();
-                if (cch < 3) tmem_ld32(s_addr + (cch + 1) * 32, buf[(cch + 1) & 1]);
-                if (diagonal) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (cch * 32 + i >= keys_visible) buf[cch & 1][i] = __float_as_uint(-CUDART_INF_F);
-                }
                 uint32_t preg[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float2 x = ffma2(make_float2(__uint_as_float(buf[cch & 1][2 * i]),
-                                                       __uint_as_float(buf[cch & 1][2 * i + 1])), c2, negm2);
-                    const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                    const float2 x = ffma2(make_float2(__uint_as_float(sreg[cch][2 * i]), __uint_as_float(sreg[cch][2 * i + 1])),
+                                           c2, negm2);
+                    const float2 p = (i & 7) < kPolyPairsOf8 ? exp2_poly_pair(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
                     sum2[i & 3] = fadd2(sum2[i & 3], p);
                     preg[i] = pack_bf16x2(p.x, p.y);
                 }
