@@ -7,14 +7,10 @@
 //
 // One warp owns one (token, head) row of 128 values: lane l holds dimensions
 // 4l..4l+3 (one 8-byte load/store per row, 256 B per warp).  The arithmetic
-// keeps the reference's five bf16 roundings per element and reproduces its
-// sum-of-squares reduction order, so the output bits equal the reference
-// kernel's: the reference reduces 128 per-thread squares with a shuffle-down
-// tree inside each 32-thread warp and then folds the four warp sums as
-// (w0 + w2) + (w1 + w3).  Here the 32 values of "warp" j sit in lanes 8j..8j+7,
-// and the same pairs are added in the same order with xor shuffles (float
-// addition commutes, so a + b from either side is the same value).
-#include "qm_common.cuh"
+// (qm_norm_rope.cuh) keeps the reference's five bf16 roundings per element,
+// its rsqrtf and its sum-of-squares reduction order, so the output bits equal
+// the reference kernel's.
+#include "qm_norm_rope.cuh"
 
 namespace {
 
@@ -45,30 +41,6 @@ struct AppendArgs {
     int kv_heads;
     float epsilon;
 };
-
-__device__ __forceinline__ float reference_order_sum_of_squares(float s0, float s1, float s2, float s3) {
-    // Tree inside the 8-lane group holding one reference warp's 32 values.
-    s0 += __shfl_xor_sync(0xffffffffu, s0, 4);
-    s1 += __shfl_xor_sync(0xffffffffu, s1, 4);
-    s2 += __shfl_xor_sync(0xffffffffu, s2, 4);
-    s3 += __shfl_xor_sync(0xffffffffu, s3, 4);
-    s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
-    s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
-    s2 += __shfl_xor_sync(0xffffffffu, s2, 2);
-    s3 += __shfl_xor_sync(0xffffffffu, s3, 2);
-    s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
-    s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
-    s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
-    s3 += __shfl_xor_sync(0xffffffffu, s3, 1);
-    s0 = __fadd_rn(s0, s2);
-    s1 = __fadd_rn(s1, s3);
-    const float warp_sum = __fadd_rn(s0, s1);      // exact in lanes 0, 8, 16, 24
-    const float w0 = __shfl_sync(0xffffffffu, warp_sum, 0);
-    const float w1 = __shfl_sync(0xffffffffu, warp_sum, 8);
-    const float w2 = __shfl_sync(0xffffffffu, warp_sum, 16);
-    const float w3 = __shfl_sync(0xffffffffu, warp_sum, 24);
-    return __fadd_rn(__fadd_rn(w0, w2), __fadd_rn(w1, w3));
-}
 
 // R consecutive head rows of the same token per warp (R divides q_heads + kv_heads): one stream / position
 // lookup and R independent 256-byte loads in flight per warp.
@@ -147,30 +119,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32) qm_norm_rope_append_kernel(
         const int slot = slot0 + r;
         const bool is_query = slot < a.q_heads;
         const int head = is_query ? slot : slot - a.q_heads;
-        const uint2 wraw = is_query ? qwraw : kwraw;
-        const float x[4] = {bf16_lo(raw[r].x), bf16_hi(raw[r].x), bf16_lo(raw[r].y), bf16_hi(raw[r].y)};
-        const float w[4] = {bf16_lo(wraw.x), bf16_hi(wraw.x), bf16_lo(wraw.y), bf16_hi(wraw.y)};
-
-        const float sum = reference_order_sum_of_squares(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]),
-                                                         __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
-        const float inverse_rms = rsqrtf(__fadd_rn(__fdiv_rn(sum, (float)kHeadDim), a.epsilon));
-
-        // RMSNorm: normalise in fp32 -> bf16 -> multiply by the bf16 weight -> bf16.
-        float n[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) n[i] = round_bf16(__fmul_rn(round_bf16(__fmul_rn(x[i], inverse_rms)), w[i]));
-
-        // rotate_half: dimension d pairs with d +- 64, which lane l ^ 16 holds.
-        uint32_t out_bits[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float partner = __shfl_xor_sync(0xffffffffu, n[i], 16);
-            if (lane < 16) partner = -partner;
-            const float first = round_bf16(__fmul_rn(n[i], c[i]));
-            const float second = round_bf16(__fmul_rn(partner, s[i]));
-            out_bits[i] = f32_to_bf16_bits(__fadd_rn(first, second));
-        }
-        const uint2 packed = make_uint2(out_bits[0] | (out_bits[1] << 16), out_bits[2] | (out_bits[3] << 16));
+        const uint2 packed = norm_rope_row(raw[r], is_query ? qwraw : kwraw, c, s, lane, a.epsilon);
 
         if (is_query) {
             *reinterpret_cast<uint2*>(a.q_rot + ((size_t)token * a.q_heads + head) * kHeadDim + 4 * lane) = packed;
