@@ -166,6 +166,21 @@ int32_t qm_decode_attention(qm_kv_pool* pool, int32_t layer, const uint16_t* q_r
                             const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads,
                             uint16_t* out, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* The whole decode step of one layer in ONE launch: launch_qk_norm_rope_cache_m1
+ * (17.cu:17741) followed by launch_attention (17.cu:17895), as decode_device
+ * issues them (17.cu:17284-17309).  Inputs are those of qm_decode_append_rope
+ * (raw q, k, v projections, norm weights, RoPE table, positions); every stream
+ * attends positions[s] + 1 keys.  QK-RMSNorm and RoPE are applied as q and the
+ * new k row are loaded; the new K (normed, roped) and V (raw) rows are written
+ * to the pool for later steps and used from shared memory in this one.  The
+ * bits written to the pool and the context equal those of the two separate
+ * calls.  No q_rot buffer is produced. */
+int32_t qm_decode_step(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                       const uint16_t* q_norm_weight, const uint16_t* k_norm_weight, const uint16_t* rope_cos,
+                       const uint16_t* rope_sin, int32_t rope_rows, const int32_t* positions,
+                       const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads, float epsilon,
+                       uint16_t* out, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Decode attention without any allocation, here or in the caller.  No counterpart
  * in the reference, whose engine allocates all workspace at construction.
  * Same inputs, outputs and result as qm_decode_attention, but the scratch

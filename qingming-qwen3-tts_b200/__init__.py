@@ -66,6 +66,8 @@ ABI = {
     "qm_decode_workspace_init": (c_int32, [c_void_p, c_int64, c_void_p]),
     "qm_decode_attention": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                       c_void_p, c_void_p, c_int64, c_void_p]),
+    "qm_decode_step": (c_int32, [c_void_p, c_int32] + [c_void_p] * 7 + [c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32,
+                                                                    c_float, c_void_p, c_void_p, c_int64, c_void_p]),
     "qm_decode_attention_static": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
                                              c_int32, c_void_p, c_void_p]),
     "qm_decode_attention_partial": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
@@ -241,6 +243,20 @@ class TalkerAttention:
         _check(self.lib.qm_decode_attention(self.pool, layer, _ptr(q_rot), _ptr(seq_lens), _ptr(page_table),
                                             page_table.shape[1], batch, self.q_heads, _ptr(out), _ptr(ws),
                                             ws.numel(), _stream()))
+        return out
+
+    def decode_step(self, layer, q, k, v, q_norm_weight, k_norm_weight, positions, page_table, out=None):
+        """launch_qk_norm_rope_cache_m1 + launch_attention of one layer in a single launch."""
+        import torch
+
+        batch = q.shape[0]
+        if out is None:
+            out = torch.empty_like(q)
+        ws = self.workspace(batch)
+        _check(self.lib.qm_decode_step(
+            self.pool, layer, _ptr(q), _ptr(k), _ptr(v), _ptr(q_norm_weight), _ptr(k_norm_weight), _ptr(self.rope_cos),
+            _ptr(self.rope_sin), self.max_positions, _ptr(positions), _ptr(page_table), page_table.shape[1], batch,
+            self.q_heads, self.epsilon, _ptr(out), _ptr(ws), ws.numel(), _stream()))
         return out
 
     def launch_attention_static(self, layer, q_rot, seq_lens, page_table, out=None):

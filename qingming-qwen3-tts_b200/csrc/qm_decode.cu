@@ -28,14 +28,16 @@
 
 #include <mutex>
 
-#include "qm_common.cuh"
+#include "qm_norm_rope.cuh"
 
 namespace {
 
 constexpr int kStages = 3;
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kDecodeThreads = kConsumerThreads + 32;
+constexpr int kProducerWarp = kConsumerWarps;          // issues every bulk copy
+constexpr int kPrepWarp = kConsumerWarps + 1;          // fused step: QK-RMSNorm + RoPE of the staged rows
+constexpr int kDecodeThreads = kConsumerThreads + 64;
 constexpr int kStageBytes = 2 * kTileBytes;
 constexpr int kMaxBatchPerLaunch = 512;
 constexpr int kMaxGrid = 1024;
@@ -44,10 +46,20 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
 struct DecodeArgs {
-    const uint16_t* q_rot;
-    const uint16_t* key_pool;
-    const uint16_t* value_pool;
-    const int32_t* seq_lens;
+    const uint16_t* q_rot;       // normed + roped queries; in the fused step: the raw q projections
+    uint16_t* key_pool;
+    uint16_t* value_pool;
+    const int32_t* seq_lens;     // keys to attend; in the fused step: positions (keys = position + 1)
+    // fused step only: raw k / v projections of the new token, norm weights, RoPE table
+    const uint16_t* raw_k;
+    const uint16_t* raw_v;
+    const uint16_t* q_norm_weight;
+    const uint16_t* k_norm_weight;
+    const uint16_t* rope_cos;
+    const uint16_t* rope_sin;
+    int rope_rows;
+    int len_offset;              // 0, or 1 in the fused step
+    float epsilon;
     const int32_t* page_table;
     uint16_t* out;           // mode 0
     float* partial_out;      // mode 1: [batch][q_heads][130]
@@ -66,10 +78,12 @@ struct SharedLayout {
     static constexpr int kScoreOff = kPrefixOff + ((kMaxBatchPerLaunch + 1) * 4 + 15) / 16 * 16;
     static constexpr int kMergeOff = kScoreOff + 2 * 2 * kPageTokens * 4;          // float[2][2][64]
     static constexpr int kMergeLOff = kMergeOff + kConsumerWarps * 2 * kHeadDim * 4;
-    static constexpr int kQOff = kMergeLOff + kConsumerWarps * 2 * 4;              // bf16[kStages][2][128]
-    static constexpr int kMetaOff = kQOff + kStages * 2 * kHeadDim * 2;
-    static constexpr int kBarOff = kMetaOff + kStages * 16;
-    static constexpr int kFlagOff = kBarOff + 2 * kStages * 8;
+    // per stage: q rows of the two heads (512 B); fused step also cos, sin, raw k, raw v rows (256 B each)
+    static constexpr int kStagingBytes = 1536;
+    static constexpr int kQOff = kMergeLOff + kConsumerWarps * 2 * 4;
+    static constexpr int kMetaOff = kQOff + kStages * kStagingBytes;
+    static constexpr int kBarOff = kMetaOff + kStages * 32;
+    static constexpr int kFlagOff = kBarOff + 3 * kStages * 8;
     static constexpr int kTotal = kFlagOff + 16;
 };
 
@@ -83,17 +97,19 @@ __device__ __forceinline__ int clamp_len(int len, int max_pages, uint32_t* statu
     return len;
 }
 
+template <bool kFused>
 __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(const DecodeArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     int32_t* prefix = reinterpret_cast<int32_t*>(smem + SharedLayout::kPrefixOff);
     float* score = reinterpret_cast<float*>(smem + SharedLayout::kScoreOff);
     float* merge_o = reinterpret_cast<float*>(smem + SharedLayout::kMergeOff);
     float* merge_l = reinterpret_cast<float*>(smem + SharedLayout::kMergeLOff);
-    int4* meta = reinterpret_cast<int4*>(smem + SharedLayout::kMetaOff);
+    int4* meta = reinterpret_cast<int4*>(smem + SharedLayout::kMetaOff);      // two int4 per stage
     volatile int* fold_flag = reinterpret_cast<volatile int*>(smem + SharedLayout::kFlagOff);
     const uint32_t bar_base = smem_addr(smem + SharedLayout::kBarOff);
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto staged_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -103,8 +119,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
     pdl_trigger();
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(full_bar(s), 1);
+            mbar_init(full_bar(s), kFused ? 2 : 1);       // producer (+ bytes) and, in the fused step, the prep warp
             mbar_init(empty_bar(s), kConsumerWarps);
+            mbar_init(staged_bar(s), 1);
         }
         fence_mbar_init();
     }
@@ -112,7 +129,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
 
     // Units per stream, then an inclusive scan -> prefix[s] = first unit of stream s.
     for (int s = tid; s < a.batch; s += kDecodeThreads) {
-        const int len = clamp_len(a.seq_lens[s], a.max_pages, a.status);
+        const int len = clamp_len(a.seq_lens[s] + a.len_offset, a.max_pages, a.status);
         prefix[s + 1] = ((len + kPageTokens - 1) >> 6) * hkv;
     }
     if (tid == 0) prefix[0] = 0;
@@ -163,7 +180,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
 
     bool dead = false;
 
-    if (warp == kConsumerWarps) {
+    if (warp == kProducerWarp) {
         // ------------------------------------------------------------ producer
         for (int base = 0; base < count; base += 32) {
             int seg_l = 0, page_idx_l = 0, pages_l = 1, page_id_l = 0, nvalid_l = 0, head_l = 0;
@@ -180,7 +197,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                 head_l = r / pages_l;
                 page_idx_l = r - head_l * pages_l;
                 seg_l = s * hkv + head_l;
-                const int len = clamp_len(a.seq_lens[s], a.max_pages, a.status);
+                const int len = clamp_len(a.seq_lens[s] + a.len_offset, a.max_pages, a.status);
                 const int left = len - page_idx_l * kPageTokens;
                 nvalid_l = left < kPageTokens ? left : kPageTokens;
                 page_id_l = a.page_table[(size_t)s * a.max_pages + page_idx_l];
@@ -202,18 +219,50 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                     const int stage = n % kStages;
                     const uint32_t parity = ((n / kStages) & 1) ^ 1;
                     if (!mbar_wait_bounded(empty_bar(stage), parity, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
-                    meta[stage] = make_int4(seg, page_idx, pages, nvalid);
-                    const uint32_t bytes = (uint32_t)nvalid * kHeadDim * 2;
+                    meta[2 * stage] = make_int4(seg, page_idx, pages, nvalid);
+                    meta[2 * stage + 1] = make_int4(page_id, 0, 0, 0);
                     const size_t tile = ((size_t)page_id * hkv + head) * kTileElems;
                     const uint32_t dst = smem_addr(smem + stage * kStageBytes);
+                    const uint32_t staging = smem_addr(smem + SharedLayout::kQOff + stage * SharedLayout::kStagingBytes);
                     const bool new_segment = n == 0 || page_idx == 0;
                     constexpr uint32_t kQBytes = 2 * kHeadDim * 2;         // the two query heads of this KV head
-                    mbar_arrive_expect_tx(full_bar(stage), 2 * bytes + (new_segment ? kQBytes : 0u));
-                    if (new_segment)
-                        bulk_copy_g2s(smem_addr(smem + SharedLayout::kQOff + stage * kQBytes),
-                                      a.q_rot + (size_t)seg * 2 * kHeadDim, kQBytes, full_bar(stage));
-                    bulk_copy_g2s(dst, a.key_pool + tile, bytes, full_bar(stage));
-                    bulk_copy_g2s(dst + kTileBytes, a.value_pool + tile, bytes, full_bar(stage));
+                    constexpr uint32_t kRowBytes = kHeadDim * 2;
+                    if (!kFused) {
+                        const uint32_t bytes = (uint32_t)nvalid * kRowBytes;
+                        mbar_arrive_expect_tx(full_bar(stage), 2 * bytes + (new_segment ? kQBytes : 0u));
+                        if (new_segment) bulk_copy_g2s(staging, a.q_rot + (size_t)seg * 2 * kHeadDim, kQBytes, full_bar(stage));
+                        bulk_copy_g2s(dst, a.key_pool + tile, bytes, full_bar(stage));
+                        bulk_copy_g2s(dst + kTileBytes, a.value_pool + tile, bytes, full_bar(stage));
+                    } else {
+                        // The last page of a segment ends with the new token, which is not in the pool yet: its
+                        // row is built by the consumers from the raw k / v rows staged here.
+                        const bool last_page = page_idx == pages - 1;
+                        const uint32_t bytes = (uint32_t)(last_page ? nvalid - 1 : nvalid) * kRowBytes;
+                        const int stream = seg / hkv;
+                        int position = a.seq_lens[stream];
+                        if (position < 0 || position >= a.rope_rows) {
+                            atomicOr(a.status, QM_DEVSTAT_BAD_POS);
+                            position = position < 0 ? 0 : a.rope_rows - 1;
+                        }
+                        const bool needs_rope = new_segment || last_page;
+                        // small rows first, on their own barrier: the prep warp works on them while the tile lands
+                        mbar_arrive_expect_tx(staged_bar(stage), (new_segment ? kQBytes : 0u) + (needs_rope ? 2 * kRowBytes : 0u) +
+                                                                     (last_page ? 2 * kRowBytes : 0u));
+                        if (new_segment) bulk_copy_g2s(staging, a.q_rot + (size_t)seg * 2 * kHeadDim, kQBytes, staged_bar(stage));
+                        if (needs_rope) {
+                            bulk_copy_g2s(staging + 512, a.rope_cos + (size_t)position * kHeadDim, kRowBytes, staged_bar(stage));
+                            bulk_copy_g2s(staging + 768, a.rope_sin + (size_t)position * kHeadDim, kRowBytes, staged_bar(stage));
+                        }
+                        if (last_page) {
+                            bulk_copy_g2s(staging + 1024, a.raw_k + (size_t)seg * kHeadDim, kRowBytes, staged_bar(stage));
+                            bulk_copy_g2s(staging + 1280, a.raw_v + (size_t)seg * kHeadDim, kRowBytes, staged_bar(stage));
+                        }
+                        mbar_arrive_expect_tx(full_bar(stage), 2 * bytes);
+                        if (bytes) {
+                            bulk_copy_g2s(dst, a.key_pool + tile, bytes, full_bar(stage));
+                            bulk_copy_g2s(dst + kTileBytes, a.value_pool + tile, bytes, full_bar(stage));
+                        }
+                    }
                 }
                 __syncwarp();
             }
@@ -225,6 +274,56 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
             bool ignore = false;
             const int first = count > kStages ? count - kStages : 0;
             for (int n = first; n < count; ++n) mbar_wait_bounded(full_bar(n % kStages), (n / kStages) & 1, ignore);
+        }
+        return;
+    }
+
+    if (warp == kPrepWarp) {
+        // ------------------------------------------------- fused step: norm + RoPE of the staged rows
+        // For every unit: wait for the producer's small rows, turn the raw q rows into q_rot in place (new
+        // segment), build the new token's K row (normed, roped) and copy its V row into the shared-memory tile
+        // and into the pool (last page of a segment), then arrive on the unit's full barrier.  The consumers
+        // find everything in place when that barrier completes.
+        if (kFused) {
+            const uint2 wq = *reinterpret_cast<const uint2*>(a.q_norm_weight + 4 * lane);
+            const uint2 wk = *reinterpret_cast<const uint2*>(a.k_norm_weight + 4 * lane);
+            for (int n = 0; n < count; ++n) {
+                const int stage = n % kStages;
+                if (!mbar_wait_bounded(staged_bar(stage), (n / kStages) & 1, dead) && lane == 0)
+                    atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                const int4 mt = meta[2 * stage];
+                const int seg = mt.x, page_idx = mt.y, pages = mt.z, nvalid = mt.w;
+                const int head = seg % hkv;
+                const bool new_segment = n == 0 || page_idx == 0;
+                const bool last_page = page_idx == pages - 1;
+                unsigned char* staging = smem + SharedLayout::kQOff + stage * SharedLayout::kStagingBytes;
+                if (new_segment || last_page) {
+                    const uint2 craw = *reinterpret_cast<const uint2*>(staging + 512 + lane * 8);
+                    const uint2 sraw = *reinterpret_cast<const uint2*>(staging + 768 + lane * 8);
+                    const float c[4] = {bf16_lo(craw.x), bf16_hi(craw.x), bf16_lo(craw.y), bf16_hi(craw.y)};
+                    const float sn[4] = {bf16_lo(sraw.x), bf16_hi(sraw.x), bf16_lo(sraw.y), bf16_hi(sraw.y)};
+                    if (new_segment) {
+#pragma unroll
+                        for (int h2 = 0; h2 < 2; ++h2) {
+                            uint2* row = reinterpret_cast<uint2*>(staging + h2 * 256 + lane * 8);
+                            *row = norm_rope_row(*row, wq, c, sn, lane, a.epsilon);
+                        }
+                    }
+                    if (last_page) {
+                        const uint2 krow = norm_rope_row(*reinterpret_cast<const uint2*>(staging + 1024 + lane * 8), wk, c, sn,
+                                                         lane, a.epsilon);
+                        const uint2 vrow = *reinterpret_cast<const uint2*>(staging + 1280 + lane * 8);
+                        const size_t elem = (((size_t)meta[2 * stage + 1].x * hkv + head) * kPageTokens + (nvalid - 1)) * kHeadDim + 4 * lane;
+                        unsigned char* tile_row = smem + stage * kStageBytes + (nvalid - 1) * (kHeadDim * 2) + lane * 8;
+                        *reinterpret_cast<uint2*>(tile_row) = krow;
+                        *reinterpret_cast<uint2*>(tile_row + kTileBytes) = vrow;
+                        *reinterpret_cast<uint2*>(a.key_pool + elem) = krow;
+                        *reinterpret_cast<uint2*>(a.value_pool + elem) = vrow;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_bar(stage));
+            }
         }
         return;
     }
@@ -242,17 +341,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
         const int stage = n % kStages;
         if (!mbar_wait_bounded(full_bar(stage), (n / kStages) & 1, dead) && lane == 0)
             atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
-        const int4 mt = meta[stage];
+        const int4 mt = meta[2 * stage];
         const int seg = mt.x, page_idx = mt.y, pages = mt.z, nvalid = mt.w;
+        unsigned char* staging = smem + SharedLayout::kQOff + stage * SharedLayout::kStagingBytes;
         const int stream = seg / hkv;
         const int head = seg - stream * hkv;
 
         if (n == 0 || page_idx == 0) {
-            // New segment: fetch the two query heads of this KV head.
-            // The producer staged q_rot rows (2*head, 2*head+1) of this stream beside the tile.
+            // New segment: fetch the two query heads of this KV head (q_rot rows 2*head, 2*head+1 of this
+            // stream, staged beside the tile by the producer).
             const float qscale = kLog2e / sqrtf((float)kHeadDim);
             const float2 qs2 = make_float2(qscale, qscale);
-            const unsigned char* qp = smem + SharedLayout::kQOff + stage * (2 * kHeadDim * 2) + lp * 16;
+            const unsigned char* qp = staging + lp * 16;
             const uint4 qa = *reinterpret_cast<const uint4*>(qp);
             const uint4 qb = *reinterpret_cast<const uint4*>(qp + kHeadDim * 2);
             q0[0] = fmul2(bf16x2_to_float2(qa.x), qs2); q0[1] = fmul2(bf16x2_to_float2(qa.y), qs2);
@@ -479,9 +579,22 @@ __global__ void __launch_bounds__(128) qm_combine_partials_kernel(const float* _
 
 size_t partials_bytes(int segments) { return (size_t)(kMaxGrid + segments) * 2 * kPartialStride * sizeof(float); }
 
+// Extra inputs of the fused step (append + attention in one launch); null for plain attention.
+struct FusedInputs {
+    const uint16_t* k;
+    const uint16_t* v;
+    const uint16_t* q_norm_weight;
+    const uint16_t* k_norm_weight;
+    const uint16_t* rope_cos;
+    const uint16_t* rope_sin;
+    int rope_rows;
+    float epsilon;
+};
+
 int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const int32_t* seq_lens,
                    const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads, uint16_t* out,
-                   float* partial_out, void* workspace, int64_t workspace_bytes, cudaStream_t stream, int mode) {
+                   float* partial_out, void* workspace, int64_t workspace_bytes, cudaStream_t stream, int mode,
+                   const FusedInputs* fused = nullptr) {
     if (!pool) return qm_fail(QM_EINVAL, "pool is null");
     if (layer < 0 || layer >= pool->layers) return qm_fail(QM_EINVAL, "layer out of range");
     if (!q_rot || !seq_lens || !page_table || !workspace || (mode == 0 ? !out : !partial_out))
@@ -497,7 +610,10 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
 
     static thread_local int attr_device = -1;
     if (attr_device != pool->device) {
-        QM_CUDA_TRY(cudaFuncSetAttribute(qm_decode_splitkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        QM_CUDA_TRY(cudaFuncSetAttribute(qm_decode_splitkv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SharedLayout::kTotal),
+                    "raise decode kernel shared memory");
+        QM_CUDA_TRY(cudaFuncSetAttribute(qm_decode_splitkv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SharedLayout::kTotal),
                     "raise decode kernel shared memory");
         attr_device = pool->device;
@@ -518,6 +634,15 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
     a.max_pages = max_pages;
     a.num_pages = pool->num_pages;
     a.mode = mode;
+    if (fused) {
+        a.q_norm_weight = fused->q_norm_weight;
+        a.k_norm_weight = fused->k_norm_weight;
+        a.rope_cos = fused->rope_cos;
+        a.rope_sin = fused->rope_sin;
+        a.rope_rows = fused->rope_rows;
+        a.epsilon = fused->epsilon;
+        a.len_offset = 1;
+    }
     for (int begin = 0; begin < batch; begin += chunk_cap) {
         const int n = batch - begin < chunk_cap ? batch - begin : chunk_cap;
         a.q_rot = q_rot + (size_t)begin * q_heads * kHeadDim;
@@ -526,8 +651,17 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
         a.out = out ? out + (size_t)begin * q_heads * kHeadDim : nullptr;
         a.partial_out = partial_out ? partial_out + (size_t)begin * q_heads * kPartialStride : nullptr;
         a.batch = n;
-        QM_CUDA_TRY(qm_launch(qm_decode_splitkv_kernel, dim3(grid), dim3(kDecodeThreads), SharedLayout::kTotal, stream, a),
-                    "split-KV decode attention launch");
+        if (fused) {
+            a.raw_k = fused->k + (size_t)begin * pool->kv_heads * kHeadDim;
+            a.raw_v = fused->v + (size_t)begin * pool->kv_heads * kHeadDim;
+            QM_CUDA_TRY(qm_launch(qm_decode_splitkv_kernel<true>, dim3(grid), dim3(kDecodeThreads), SharedLayout::kTotal,
+                                  stream, a),
+                        "fused decode step launch");
+        } else {
+            QM_CUDA_TRY(qm_launch(qm_decode_splitkv_kernel<false>, dim3(grid), dim3(kDecodeThreads), SharedLayout::kTotal,
+                                  stream, a),
+                        "split-KV decode attention launch");
+        }
     }
     return QM_OK;
 }
@@ -554,6 +688,24 @@ int32_t qm_decode_attention(qm_kv_pool* pool, int32_t layer, const uint16_t* q_r
                             uint16_t* out, void* workspace, int64_t workspace_bytes, void* stream) {
     return run_decode(pool, layer, q_rot, seq_lens, page_table, max_pages, batch, q_heads, out, nullptr, workspace,
                       workspace_bytes, static_cast<cudaStream_t>(stream), 0);
+}
+
+int32_t qm_decode_step(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                       const uint16_t* q_norm_weight, const uint16_t* k_norm_weight, const uint16_t* rope_cos,
+                       const uint16_t* rope_sin, int32_t rope_rows, const int32_t* positions,
+                       const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads, float epsilon,
+                       uint16_t* out, void* workspace, int64_t workspace_bytes, void* stream) {
+    if (!k || !v || !q_norm_weight || !k_norm_weight || !rope_cos || !rope_sin)
+        return qm_fail(QM_EINVAL, "null tensor pointer");
+    if (rope_rows < 1) return qm_fail(QM_EINVAL, "invalid geometry");
+    const uintptr_t all = reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                          reinterpret_cast<uintptr_t>(rope_cos) | reinterpret_cast<uintptr_t>(rope_sin);
+    if (all & 15u) return qm_fail(QM_EINVAL, "k, v and the RoPE table must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(q_norm_weight) | reinterpret_cast<uintptr_t>(k_norm_weight)) & 7u)
+        return qm_fail(QM_EINVAL, "norm weights must be 8-byte aligned");
+    const FusedInputs fused{k, v, q_norm_weight, k_norm_weight, rope_cos, rope_sin, rope_rows, epsilon};
+    return run_decode(pool, layer, q, positions, page_table, max_pages, batch, q_heads, out, nullptr, workspace,
+                      workspace_bytes, static_cast<cudaStream_t>(stream), 0, &fused);
 }
 
 int32_t qm_decode_attention_partial(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot,
