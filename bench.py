@@ -345,6 +345,11 @@ def run_ours(args):
     # the timed region launches this one kernel LAYERS times per step and nothing else, so its average launch
     # duration there is the step time over LAYERS; the per-launch event samples (launches serialised by the
     # events between them) are reported beside it
+    traffic = None
+    traffic_file = ROOT / "profiles" / "decode_step_traffic.txt"
+    if traffic_file.exists():          # dram read + write per launch of this kernel on this workload, from one ncu capture
+        t = json.loads(traffic_file.read_text())
+        traffic = t["dram_bytes_read"] + t["dram_bytes_write"]
     launch_ms = ms_per_step / LAYERS
     achieved = attn_bytes / (launch_ms * 1e-3) / 1e9
 
@@ -368,7 +373,7 @@ def run_ours(args):
         "gpu_launches": args.steps * LAYERS,
         "roofline": {"bound": "hbm", "kernel": "qm_decode_splitkv_kernel<fused>", "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "bytes_per_launch": attn_bytes, "us_per_launch": launch_ms * 1e3,
+                     "traffic": traffic, "bytes_per_launch": attn_bytes, "us_per_launch": launch_ms * 1e3,
                      "us_per_launch_isolated": attn_ms * 1e3},
         "clocks": clocks,
         "device_status": status,
