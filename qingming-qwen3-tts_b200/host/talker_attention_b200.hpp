@@ -99,6 +99,16 @@ public:
               "Talker GQA2 M1 attention launch");
     }
 
+    // launch_qk_norm_rope_cache_m1 + launch_attention of one layer in a single launch (same bits).
+    void decode_step(int layer, const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* q_norm,
+                     const uint16_t* k_norm, const int32_t* positions, const int32_t* page_table, int max_pages,
+                     int batch, uint16_t* context) {
+        check(qm_decode_step(pool_, layer, q, k, v, q_norm, k_norm, rope_cos_.as<uint16_t>(), rope_sin_.as<uint16_t>(),
+                             rope_rows_, positions, page_table, max_pages, batch, q_heads_, 1.0e-6f, context,
+                             workspace_.pointer, static_cast<int64_t>(workspace_.bytes), stream_),
+              "Talker fused decode step launch");
+    }
+
     // Prefill: launch_rmsnorm(q), launch_rmsnorm(k), launch_rope_rows(q), launch_rope_rows(k),
     // scatter_prefill_cache in one launch over packed varlen rows.
     void scatter_prefill_cache(int layer, const uint16_t* q, const uint16_t* k, const uint16_t* v,
