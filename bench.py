@@ -393,6 +393,13 @@ def run_ours(args):
         line["prefill"] = prefill
     if not args.no_long_context:
         line["long_context"] = run_long_context_section(pkg, world, rank, args.steps)
+    if not args.no_talker_step:
+        talker = run_talker_step_section(pkg, args.steps)
+        if world > 1:
+            t = torch.tensor([talker["tokens_per_s"]], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t)
+            talker["tokens_per_s_all_gpus"] = float(t.item())
+        line["talker_step"] = talker
     if rank == 0:
         print(json.dumps(line))
     eng.close()
@@ -470,6 +477,112 @@ def run_prefill_section(pkg, steps, warmup, n_seqs=8):
     }
     eng.close()
     return result
+
+
+def run_talker_step_section(pkg, steps):
+    """Secondary measurement: one greedy decode step of a random-init Qwen3 decoder in the 1.7B talker shape
+    (28 layers, hidden 2048, 16 q / 8 kv heads, head_dim 128, SwiGLU 6144, RMSNorm, QK-norm, RoPE 1e6, codec vocab
+    3072), 32 streams per GPU at context 2048.  The attention path of every layer is qm_decode_step; everything
+    else (projections, MLP, norms, head, argmax) is plain library code (torch / cuBLAS) that only exists to put the
+    attention path into a whole step - it is not part of the product.  The step is captured in one CUDA graph."""
+    import torch
+    import torch.nn.functional as F
+
+    hidden, inter, vocab, layers, streams, context = 2048, 6144, 3072, 28, 32, 2048
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(4000)
+
+    def weight(*shape):
+        return (torch.randn(*shape, generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+
+    w_qkv = [weight((Q_HEADS + 2 * KV_HEADS) * D, hidden) for _ in range(layers)]
+    w_o = [weight(hidden, Q_HEADS * D) for _ in range(layers)]
+    w_gate_up = [weight(2 * inter, hidden) for _ in range(layers)]
+    w_down = [weight(hidden, inter) for _ in range(layers)]
+    norm1 = [torch.ones(hidden, dtype=torch.bfloat16, device="cuda") for _ in range(layers)]
+    norm2 = [torch.ones(hidden, dtype=torch.bfloat16, device="cuda") for _ in range(layers)]
+    final_norm = torch.ones(hidden, dtype=torch.bfloat16, device="cuda")
+    head = weight(vocab, hidden)
+    embed = weight(vocab, hidden)
+    ones = torch.ones(D, dtype=torch.bfloat16, device="cuda")
+
+    max_new = 64
+    pages_per_stream = (context + max_new + PAGE - 1) // PAGE
+    num_pages = streams * pages_per_stream
+    eng = pkg.TalkerAttention(layers=layers, num_pages=num_pages, q_heads=Q_HEADS, kv_heads=KV_HEADS,
+                              max_positions=context + max_new + 1)
+    for layer in range(layers):
+        for view in eng.pool_view(layer):
+            view.normal_(generator=gen)
+    page_table = torch.randperm(num_pages, generator=gen, device="cuda").to(torch.int32).view(streams, pages_per_stream)
+    positions = torch.full((streams,), context, dtype=torch.int32, device="cuda")
+    tokens = torch.randint(0, vocab, (streams,), generator=gen, device="cuda")
+    eng.workspace(streams)
+    attn_out = torch.empty((streams, Q_HEADS, D), dtype=torch.bfloat16, device="cuda")
+    nq, nk = Q_HEADS * D, KV_HEADS * D
+
+    def one_step(with_attention=True):
+        x = embed[tokens]
+        for layer in range(layers):
+            h = F.rms_norm(x, (hidden,), norm1[layer], 1e-6)
+            qkv = h @ w_qkv[layer].t()
+            q = qkv[:, :nq].contiguous().view(streams, Q_HEADS, D)
+            k = qkv[:, nq:nq + nk].contiguous().view(streams, KV_HEADS, D)
+            v = qkv[:, nq + nk:].contiguous().view(streams, KV_HEADS, D)
+            if with_attention:
+                eng.decode_step(layer, q, k, v, ones, ones, positions, page_table, out=attn_out)
+            x = x + attn_out.view(streams, nq) @ w_o[layer].t()
+            h = F.rms_norm(x, (hidden,), norm2[layer], 1e-6)
+            gu = h @ w_gate_up[layer].t()
+            x = x + (F.silu(gu[:, :inter]) * gu[:, inter:]) @ w_down[layer].t()
+        logits = F.rms_norm(x, (hidden,), final_norm, 1e-6) @ head.t()
+        tokens.copy_(torch.argmax(logits.float(), dim=-1))
+        positions.add_(1)
+
+    def capture(with_attention):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                one_step(with_attention)
+            positions.fill_(context)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            one_step(with_attention)
+        positions.fill_(context)
+        return graph
+
+    def time_graph(graph, n):
+        for _ in range(3):
+            graph.replay()
+        positions.fill_(context)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        positions.fill_(context)
+        return a.elapsed_time(b) / n
+
+    n = max(5, min(steps, 30))
+    full_ms = time_graph(capture(True), n)
+    rest_ms = time_graph(capture(False), n)
+    status = eng.status()
+    eng.close()
+    kv_bytes = layers * streams * (context + 1) * 4096
+    weight_bytes = 2 * (layers * ((Q_HEADS + 2 * KV_HEADS) * D * hidden + hidden * Q_HEADS * D + 3 * inter * hidden) + vocab * hidden)
+    peak, _ = load_peaks()
+    return {"workload": "talker_decode_step_1p7b_shape", "streams_per_gpu": streams, "context": context,
+            "ms_per_step": full_ms, "tokens_per_s": streams / (full_ms * 1e-3),
+            "attention_ms": full_ms - rest_ms, "attention_share": (full_ms - rest_ms) / full_ms,
+            "non_attention_ms_library_ops": rest_ms, "kv_bytes_per_step": kv_bytes, "weight_bytes_per_step": weight_bytes,
+            "hbm_bound_ms": (kv_bytes + weight_bytes) / (peak * 1e9) * 1e3, "device_status": status,
+            "note": "attention = qm_decode_step; projections, MLP, norms, head and argmax are torch/cuBLAS library "
+                    "ops; whole step replayed as one CUDA graph; attention_ms = step with minus step without the "
+                    "attention launches"}
 
 
 def run_long_context_section(pkg, world, rank, steps):
@@ -574,6 +687,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the secondary prefill measurement")
     ap.add_argument("--only-prefill", action="store_true", help="run only the prefill section (profiling aid)")
     ap.add_argument("--prefill-seqs", type=int, default=8, help="with --only-prefill: use the first N prompts")
+    ap.add_argument("--no-talker-step", action="store_true", help="skip the secondary whole-decoder-step measurement")
     ap.add_argument("--no-long-context", action="store_true", help="skip the secondary split-KV long-context measurement")
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="layers per step (default: the talker's 28); a smaller value gives a small case for profiling")

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 
 TOL_MAX_ABS = 2e-2
 TOL_MEAN_REL = 1e-2
-MAX_ULP_MISMATCH_FRACTION = 0.02   # roped rows: elements allowed to differ (by exactly one bf16 ulp)
+MAX_ULP_MISMATCH_FRACTION = 0.002  # roped rows: share of elements allowed to differ from the CPU oracle
 
 
 def ulp_distance(a, b):
@@ -26,10 +26,14 @@ def ulp_distance(a, b):
 
 
 def check_roped(got, want):
-    dist = ulp_distance(got, want)
-    assert dist.max() <= 1, f"roped row differs by {dist.max()} ulp"
-    frac = float((dist != 0).mean())
-    assert frac <= MAX_ULP_MISMATCH_FRACTION, f"{frac:.4f} of elements differ by one ulp"
+    # device rsqrtf vs the oracle's 1/sqrtf flips the first rounding of a few rows; after RoPE's a*cos + b*sin
+    # the flipped ulp is an absolute error of at most one ulp of the normalised value (|x| < 8 -> 2^-5), which
+    # near a cancellation can be many ulps of the small result.  Exact equality with the reference kernels' own
+    # bits is asserted in test_golden_gpu.py.
+    diff = np.abs(oracle.bf16_to_f32(got) - oracle.bf16_to_f32(want))
+    assert diff.max() <= 2.0 ** -5, diff.max()
+    frac = float((got != want).mean())
+    assert frac <= MAX_ULP_MISMATCH_FRACTION, f"{frac:.4f} of elements differ"
     return frac
 
 
@@ -166,3 +170,9 @@ def test_reset_request_zeroes_the_pool(qm):
         k, v = eng.pool_view(layer)
         assert not k.view(torch.int16).any().item() and not v.view(torch.int16).any().item()
     eng.close()
+
+
+def test_batch_larger_than_one_launch_chunk(qm):
+    # more than 512 streams: the host splits the batch into several launches that share the workspace
+    lengths = [int(x) for x in oracle.uniform_int(555, 0, 150, 700)]
+    check_step(qm, scenario.DecodeScenario(seed=14, lengths=lengths))

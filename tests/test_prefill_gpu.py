@@ -132,3 +132,44 @@ def test_prefill_then_decode_share_the_cache(qm):
         assert m["max_abs"] <= TOL_MAX_ABS and m["mean_rel"] <= TOL_MEAN_REL, m
     finally:
         eng.close()
+
+
+def test_second_chunk_attends_the_cache_of_the_first(qm):
+    """Chunked prefill: rows of the second call start at position start_positions[s] and attend every cached key
+    before them (the reference's cache_before, 17.cu:15832-15852)."""
+    import torch
+
+    lengths = [200, 77]
+    first = [130, 64]                      # tokens of each sequence that go in with the first call
+    ps = scenario.PrefillScenario(seed=17, lengths=lengths, random_weights=True, spare_pages=2)
+    q_rot_all, kcs, vcs = ps.expected_append()
+    tb = scenario._bf16_tensor
+    eng = qm.TalkerAttention(layers=1, num_pages=ps.num_pages, max_positions=256)
+    try:
+        table = torch.from_numpy(np.maximum(ps.page_table, 0)).cuda()
+        qw, kw = tb(torch, ps.q_w), tb(torch, ps.k_w)
+
+        def rows(lo_hi):
+            idx = np.concatenate([np.arange(ps.cu_seqlens[s] + a, ps.cu_seqlens[s] + b) for s, (a, b) in enumerate(lo_hi)])
+            return idx
+
+        for part, spans in (("first", [(0, first[0]), (0, first[1])]), ("second", [(first[0], lengths[0]), (first[1], lengths[1])])):
+            idx = rows(spans)
+            n = [b - a for a, b in spans]
+            cu = torch.tensor(np.concatenate([[0], np.cumsum(n)]).astype(np.int32)).cuda()
+            start = torch.tensor(np.array([a for a, _ in spans], dtype=np.int32)).cuda()
+            q, k, v = (tb(torch, np.ascontiguousarray(x[idx])) for x in (ps.q, ps.k, ps.v))
+            q_rot = eng.prefill_norm_rope_scatter(0, q, k, v, qw, kw, cu, table, start_positions=start)
+            out = eng.launch_attention_prefill(0, q_rot, cu, table, max(n), start_positions=start)
+            torch.cuda.synchronize()
+            assert eng.status() == 0
+            got = oracle.bf16_to_f32(scenario._bits(out))
+            want = []
+            for s, (a, b) in enumerate(spans):
+                c0 = int(ps.cu_seqlens[s])
+                res = oracle.prefill_attention(q_rot_all[c0 + a:c0 + b], kcs[s], vcs[s], b - a, cache_before=a, mode="fp32")
+                want.append(res)
+            m = oracle.error_metrics(got, np.concatenate(want))
+            assert m["max_abs"] <= TOL_MAX_ABS and m["mean_rel"] <= TOL_MEAN_REL, (part, m)
+    finally:
+        eng.close()
