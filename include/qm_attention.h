@@ -82,6 +82,13 @@ int32_t qm_kv_pool_kv_heads(const qm_kv_pool* pool);
  * synchronising `stream`.  Returns QM_OK and the bits through *bits_out. */
 int32_t qm_kv_pool_status(qm_kv_pool* pool, void* stream, uint32_t* bits_out);
 
+/* Diagnostic, no counterpart in the reference (whose kernels never wait on one
+ * another): launches one small kernel that waits, with the same bounded wait
+ * the attention kernels use, for a signal that is never sent.  After about a
+ * second the wait gives up, QM_DEVSTAT_TIMEOUT appears in the status word and
+ * the kernel returns normally; the device stays usable. */
+int32_t qm_selftest_wait_timeout(qm_kv_pool* pool, void* stream);
+
 /* ---- RoPE table: make_talker_rope (17.cu:21758-21772) */
 
 /* Fills DEVICE arrays cosine/sine [rows][128] bf16 for positions

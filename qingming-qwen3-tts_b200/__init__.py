@@ -53,6 +53,7 @@ ABI = {
     "qm_kv_pool_num_pages": (c_int32, [c_void_p]),
     "qm_kv_pool_kv_heads": (c_int32, [c_void_p]),
     "qm_kv_pool_status": (c_int32, [c_void_p, c_void_p, POINTER(c_uint32)]),
+    "qm_selftest_wait_timeout": (c_int32, [c_void_p, c_void_p]),
     "qm_rope_table_fill": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_double, c_void_p]),
     "qm_decode_append_rope": (c_int32, [c_void_p, c_int32] + [c_void_p] * 7 + [c_int32, c_void_p, c_void_p, c_int32,
                                                                            c_int32, c_int32, c_float, c_void_p, c_void_p]),

@@ -153,7 +153,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // QM_DEVSTAT_TIMEOUT and carries on with uniform control flow (the data is then
 // garbage and the host sees the status bit), so no thread is left behind at a
 // later barrier.  `dead` short-circuits every wait after the first failure.
-constexpr uint32_t kWaitSpinLimit = 1u << 21;
+constexpr uint32_t kWaitSpinLimit = 1u << 19;
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, bool& dead) {
     if (dead) return false;
