@@ -247,6 +247,34 @@ int32_t qm_prefill_attention_varlen(qm_kv_pool* pool, int32_t layer, const uint1
                                     int32_t total_tokens, int32_t max_seqlen, int32_t q_heads, uint16_t* out,
                                     void* stream);
 
+/* ---- the rest of the talker decoder layer at decode time (batch of token rows) ----
+ * The reference runs these for one token per launch; here `rows` token rows (at most 64 for the projections) go
+ * through one launch.  All keep the reference's bf16 materialisation points.  `pool` supplies the device status
+ * word that bounded waits report into. */
+
+/* Row RMSNorm: code_predictor::rmsnorm_kernel via launch_rmsnorm (17.cu:8295-8357, :8927); input and final norm
+ * of decode_device (17.cu:17259, :17389).  out = bf16(bf16(x * inv_rms) * weight), bit-identical reduction order. */
+int32_t qm_rmsnorm(const uint16_t* x, const uint16_t* weight, uint16_t* out, int32_t rows, int32_t dim, float epsilon,
+                   void* stream);
+
+/* launch_add_postnorm_m1 (17.cu:17989; kernel :16258-16343): residual = bf16(hidden + attention),
+ * normalized = RMSNorm(residual) with `weight`. */
+int32_t qm_add_postnorm(const uint16_t* hidden, const uint16_t* attention, const uint16_t* weight, uint16_t* residual,
+                        uint16_t* normalized, int32_t rows, int32_t dim, float epsilon, void* stream);
+
+/* launch_linear_m1 / launch_qkv_m1 (17.cu:17646, :17691; kernels :15250-15407):
+ * out[r][n] = bf16(dot(x[r], weight[n]) + bias[n]); with `residual`, bf16(residual[r][n] + that value).
+ * weight is [out_features][in_features] row-major (q, k and v weights stacked for the fused QKV call);
+ * in_features must be a multiple of 64; bias and residual may be NULL.  tcgen05 kernel, fp32 accumulation. */
+int32_t qm_linear(qm_kv_pool* pool, const uint16_t* x, const uint16_t* weight, const uint16_t* bias,
+                  const uint16_t* residual, uint16_t* out, int32_t rows, int32_t out_features, int32_t in_features,
+                  void* stream);
+
+/* launch_gate_up_swiglu_m1 (17.cu:18020; kernel :16348-16416):
+ * out[r][c] = bf16( bf16(silu(bf16(gate))) * bf16(up) ), gate = dot(x[r], gate_weight[c]), up likewise. */
+int32_t qm_gate_up_swiglu(qm_kv_pool* pool, const uint16_t* x, const uint16_t* gate_weight, const uint16_t* up_weight,
+                          uint16_t* out, int32_t rows, int32_t hidden, int32_t intermediate, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -562,3 +562,111 @@ QMO_EXPORT void qmo_scatter_paged(const uint16_t* cache, const int32_t* page_row
         }
     }
 }
+
+/* ------------------------------------------------- rest of the talker layer */
+
+/*
+ * The non-attention operators of one talker decoder layer, row by row as the
+ * reference's M = 1 kernels compute them (the same file as above):
+ *   row RMSNorm, any width             rmsnorm_kernel                       :8295-8357
+ *   linear (+bias) (+residual)         talker_linear_fused_kernel           :15250-15317
+ *                                      talker_qkv_fused_kernel              :15321-15407
+ *   residual add + post-norm           talker_add_postnorm_fused_kernel     :16258-16343
+ *   gate/up projections + SwiGLU       talker_gate_up_swiglu_fused_kernel   :16348-16416
+ * mode 0 keeps the reference's reduction shape (lane k, k+32, ... fmaf chains, shuffle-down tree) and every
+ * bf16 materialisation; mode 1 accumulates in double and rounds only what the reference stores.
+ */
+
+static float dot_ref(const uint16_t* x, const uint16_t* w, int k_dim) {
+    float lane[32];
+    for (int l = 0; l < 32; ++l) {
+        float acc = 0.0f;
+        for (int k = l; k < k_dim; k += 32) acc = fmaf(bf16_to_f32(x[k]), bf16_to_f32(w[k]), acc);
+        lane[l] = acc;
+    }
+    return warp_tree_sum(lane);
+}
+
+static float dot_f64(const uint16_t* x, const uint16_t* w, int k_dim) {
+    double acc = 0.0;
+    for (int k = 0; k < k_dim; ++k) acc += (double)bf16_to_f32(x[k]) * (double)bf16_to_f32(w[k]);
+    return (float)acc;
+}
+
+/* out[r][n] = bf16(dot(x[r], w[n]) + bias[n]); with residual: bf16(residual[r][n] + that bf16 value). */
+QMO_EXPORT void qmo_linear(const uint16_t* x, const uint16_t* w, const uint16_t* bias, const uint16_t* residual,
+                           int rows, int n_dim, int k_dim, int mode, uint16_t* out) {
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        for (int n = 0; n < n_dim; ++n) {
+            const uint16_t* xr = x + (size_t)r * k_dim;
+            const uint16_t* wn = w + (size_t)n * k_dim;
+            float acc = mode == 0 ? dot_ref(xr, wn, k_dim) : dot_f64(xr, wn, k_dim);
+            if (bias) acc += bf16_to_f32(bias[n]);
+            uint16_t v = f32_to_bf16(acc);
+            if (residual) v = f32_to_bf16(bf16_to_f32(residual[(size_t)r * n_dim + n]) + bf16_to_f32(v));
+            out[(size_t)r * n_dim + n] = v;
+        }
+    }
+}
+
+/* Row RMSNorm of any width with the 256-thread reduction shape of rmsnorm_kernel: thread t accumulates columns
+ * t, t+256, ... with fmaf, then the block tree. */
+static float sum_squares_block256(const uint16_t* x, int dim, int use_fma) {
+    float per_thread[256];
+    for (int t = 0; t < 256; ++t) {
+        float s = 0.0f;
+        for (int c = t; c < dim; c += 256) {
+            float v = bf16_to_f32(x[c]);
+            s = use_fma ? fmaf(v, v, s) : s + v * v;
+        }
+        per_thread[t] = s;
+    }
+    return block_tree_sum(per_thread, 256);
+}
+
+QMO_EXPORT void qmo_rmsnorm(const uint16_t* x, const uint16_t* w, float eps, int rows, int dim, uint16_t* out) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const uint16_t* xr = x + (size_t)r * dim;
+        float sum = sum_squares_block256(xr, dim, 1);
+        float inv = 1.0f / sqrtf(sum / (float)dim + eps);
+        for (int c = 0; c < dim; ++c) {
+            uint16_t nb = f32_to_bf16(bf16_to_f32(xr[c]) * inv);
+            out[(size_t)r * dim + c] = f32_to_bf16(bf16_to_f32(nb) * bf16_to_f32(w[c]));
+        }
+    }
+}
+
+/* residual = bf16(hidden + attention); normalized = RMSNorm(residual) (:16258-16343). */
+QMO_EXPORT void qmo_add_postnorm(const uint16_t* hidden, const uint16_t* attention, const uint16_t* w, float eps,
+                                 int rows, int dim, uint16_t* residual, uint16_t* normalized) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const size_t base = (size_t)r * dim;
+        for (int c = 0; c < dim; ++c)
+            residual[base + c] = f32_to_bf16(bf16_to_f32(hidden[base + c]) + bf16_to_f32(attention[base + c]));
+        float sum = sum_squares_block256(residual + base, dim, 1);
+        float inv = 1.0f / sqrtf(sum / (float)dim + eps);
+        for (int c = 0; c < dim; ++c) {
+            uint16_t nb = f32_to_bf16(bf16_to_f32(residual[base + c]) * inv);
+            normalized[base + c] = f32_to_bf16(bf16_to_f32(nb) * bf16_to_f32(w[c]));
+        }
+    }
+}
+
+/* out[r][c] = bf16( bf16(silu(bf16(g))) * bf16(u) ), g = dot(x, gate[c]), u = dot(x, up[c]) (:16348-16416). */
+QMO_EXPORT void qmo_gate_up_swiglu(const uint16_t* x, const uint16_t* gate_w, const uint16_t* up_w, int rows,
+                                   int hidden, int intermediate, int mode, uint16_t* out) {
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        for (int c = 0; c < intermediate; ++c) {
+            const uint16_t* xr = x + (size_t)r * hidden;
+            float g = mode == 0 ? dot_ref(xr, gate_w + (size_t)c * hidden, hidden) : dot_f64(xr, gate_w + (size_t)c * hidden, hidden);
+            float u = mode == 0 ? dot_ref(xr, up_w + (size_t)c * hidden, hidden) : dot_f64(xr, up_w + (size_t)c * hidden, hidden);
+            float gv = rnd(g);
+            float act = rnd(gv / (1.0f + expf(-gv)));
+            out[(size_t)r * intermediate + c] = f32_to_bf16(act * rnd(u));
+        }
+    }
+}

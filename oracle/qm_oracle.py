@@ -251,3 +251,81 @@ def ref_make_rope(rows, start=0):
     sin = np.empty((rows, D), dtype=np.uint16)
     ref().qmref_make_rope(c_int(rows), c_int(start), _p(cos), _p(sin))
     return cos, sin
+
+
+# ------------------------------------------------ rest of the talker layer
+
+def scaled_normal_bf16(seed: int, shape, scale: float) -> np.ndarray:
+    """bf16 tensor ~ N(0, scale^2): the seeded N(0,1) stream times `scale`, rounded once."""
+    return f32_to_bf16(bf16_to_f32(normal_bf16(seed, shape)) * np.float32(scale))
+
+
+def linear(x, w, bias=None, residual=None, mode="ref"):
+    x, w = _u16(x), _u16(w)
+    rows, k_dim = x.shape
+    n_dim = w.shape[0]
+    out = np.empty((rows, n_dim), dtype=np.uint16)
+    lib().qmo_linear(_p(x), _p(w), _p(_u16(bias)) if bias is not None else None,
+                     _p(_u16(residual)) if residual is not None else None, c_int(rows), c_int(n_dim), c_int(k_dim),
+                     c_int(0 if mode == "ref" else 1), _p(out))
+    return out
+
+
+def rmsnorm(x, w, eps=1.0e-6):
+    x = _u16(x)
+    out = np.empty_like(x)
+    lib().qmo_rmsnorm(_p(x), _p(_u16(w)), c_float(eps), c_int(x.shape[0]), c_int(x.shape[1]), _p(out))
+    return out
+
+
+def add_postnorm(hidden, attention, w, eps=1.0e-6):
+    hidden, attention = _u16(hidden), _u16(attention)
+    residual = np.empty_like(hidden)
+    normalized = np.empty_like(hidden)
+    lib().qmo_add_postnorm(_p(hidden), _p(attention), _p(_u16(w)), c_float(eps), c_int(hidden.shape[0]),
+                           c_int(hidden.shape[1]), _p(residual), _p(normalized))
+    return residual, normalized
+
+
+def gate_up_swiglu(x, gate_w, up_w, mode="ref"):
+    x, gate_w, up_w = _u16(x), _u16(gate_w), _u16(up_w)
+    out = np.empty((x.shape[0], gate_w.shape[0]), dtype=np.uint16)
+    lib().qmo_gate_up_swiglu(_p(x), _p(gate_w), _p(up_w), c_int(x.shape[0]), c_int(x.shape[1]), c_int(gate_w.shape[0]),
+                             c_int(0 if mode == "ref" else 1), _p(out))
+    return out
+
+
+def ref_linear(x, w, bias=None, residual=None):
+    x, w = _u16(x), _u16(w)
+    out = np.empty((x.shape[0], w.shape[0]), dtype=np.uint16)
+    rc = ref().qmref_linear_rows(_p(x), _p(w), _p(_u16(bias)) if bias is not None else None,
+                                 _p(_u16(residual)) if residual is not None else None, _p(out), c_int(x.shape[0]),
+                                 c_int(w.shape[0]), c_int(x.shape[1]))
+    assert rc == 0, rc
+    return out
+
+
+def ref_rmsnorm(x, w):
+    x = _u16(x)
+    out = np.empty_like(x)
+    rc = ref().qmref_rmsnorm_rows(_p(x), _p(_u16(w)), _p(out), c_int(x.shape[0]), c_int(x.shape[1]))
+    assert rc == 0, rc
+    return out
+
+
+def ref_add_postnorm(hidden, attention, w):
+    hidden, attention = _u16(hidden), _u16(attention)
+    residual, normalized = np.empty_like(hidden), np.empty_like(hidden)
+    rc = ref().qmref_add_postnorm_rows(_p(hidden), _p(attention), _p(_u16(w)), _p(residual), _p(normalized),
+                                       c_int(hidden.shape[0]), c_int(hidden.shape[1]))
+    assert rc == 0, rc
+    return residual, normalized
+
+
+def ref_gate_up_swiglu(x, gate_w, up_w):
+    x, gate_w, up_w = _u16(x), _u16(gate_w), _u16(up_w)
+    out = np.empty((x.shape[0], gate_w.shape[0]), dtype=np.uint16)
+    rc = ref().qmref_gate_up_swiglu_rows(_p(x), _p(gate_w), _p(up_w), _p(out), c_int(x.shape[0]), c_int(x.shape[1]),
+                                         c_int(gate_w.shape[0]))
+    assert rc == 0, rc
+    return out

@@ -20,6 +20,9 @@
 //   talker_rope_rows_kernel                   :15578   launcher :17780
 //   talker_scatter_prefill_kv_kernel          :15677   launcher :17818
 //   code_predictor::rmsnorm_kernel            :8295    launcher :8927
+//   talker_linear_fused_kernel                :15250   launcher :17646
+//   talker_add_postnorm_fused_kernel          :16258   launcher :17989
+//   talker_gate_up_swiglu_fused_kernel        :16348   launcher :18020
 // Launch shapes and shared-memory sizes follow the cited launchers.
 
 #define main qm_refharness_unused_reference_main
@@ -195,6 +198,84 @@ int qmref_attention(const uint16_t* q_rot, const uint16_t* key_cache, const uint
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     RH_CHECK(cudaMemcpy(context, dctx.p, qb, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+// ---- the non-attention operators of the talker layer, one row at a time (the reference is M = 1) ----
+// Launch shapes follow launch_linear_m1 (:17646), launch_add_postnorm_m1 (:17989),
+// launch_gate_up_swiglu_m1 (:18020) and code_predictor::launch_rmsnorm (:8927).
+
+// out[r] = linear(x[r]) (+bias) (+residual[r]); weight [n_dim][k_dim].
+int qmref_linear_rows(const uint16_t* x, const uint16_t* weight, const uint16_t* bias, const uint16_t* residual,
+                      uint16_t* out, int rows, int n_dim, int k_dim) {
+    DevBuf dx, dw, db, dr, dout;
+    RH_CHECK(dx.alloc((size_t)rows * k_dim * 2)); RH_CHECK(dw.alloc((size_t)n_dim * k_dim * 2));
+    RH_CHECK(db.alloc((size_t)n_dim * 2)); RH_CHECK(dr.alloc((size_t)rows * n_dim * 2)); RH_CHECK(dout.alloc((size_t)rows * n_dim * 2));
+    RH_CHECK(cudaMemcpy(dx.p, x, dx.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dw.p, weight, dw.bytes, cudaMemcpyHostToDevice));
+    if (bias) RH_CHECK(cudaMemcpy(db.p, bias, db.bytes, cudaMemcpyHostToDevice));
+    if (residual) RH_CHECK(cudaMemcpy(dr.p, residual, dr.bytes, cudaMemcpyHostToDevice));
+    for (int r = 0; r < rows; ++r) {
+        QINGMING_CUDA_LAUNCH(rt::talker_linear_fused_kernel, dim3((unsigned)((n_dim + 15) / 16)), dim3(256), (size_t)k_dim * 2,
+                             (cudaStream_t) nullptr, dx.as<uint16_t>() + (size_t)r * k_dim, dw.as<uint16_t>(),
+                             bias ? db.as<uint16_t>() : (uint16_t*)nullptr,
+                             residual ? dr.as<uint16_t>() + (size_t)r * n_dim : (uint16_t*)nullptr,
+                             dout.as<uint16_t>() + (size_t)r * n_dim, n_dim, k_dim);
+        RH_CHECK(cudaGetLastError());
+    }
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(out, dout.p, dout.bytes, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int qmref_rmsnorm_rows(const uint16_t* x, const uint16_t* weight, uint16_t* out, int rows, int dim) {
+    DevBuf dx, dw, dout;
+    RH_CHECK(dx.alloc((size_t)rows * dim * 2)); RH_CHECK(dw.alloc((size_t)dim * 2)); RH_CHECK(dout.alloc((size_t)rows * dim * 2));
+    RH_CHECK(cudaMemcpy(dx.p, x, dx.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dw.p, weight, dw.bytes, cudaMemcpyHostToDevice));
+    rp::launch_rmsnorm(dx.as<uint16_t>(), dw.as<uint16_t>(), dout.as<uint16_t>(), rows, dim, nullptr);
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(out, dout.p, dout.bytes, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int qmref_add_postnorm_rows(const uint16_t* hidden, const uint16_t* attention, const uint16_t* weight, uint16_t* residual,
+                            uint16_t* normalized, int rows, int dim) {
+    DevBuf dh, da, dw, dr, dn;
+    const size_t bytes = (size_t)rows * dim * 2;
+    RH_CHECK(dh.alloc(bytes)); RH_CHECK(da.alloc(bytes)); RH_CHECK(dw.alloc((size_t)dim * 2)); RH_CHECK(dr.alloc(bytes)); RH_CHECK(dn.alloc(bytes));
+    RH_CHECK(cudaMemcpy(dh.p, hidden, bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(da.p, attention, bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dw.p, weight, (size_t)dim * 2, cudaMemcpyHostToDevice));
+    for (int r = 0; r < rows; ++r) {
+        const size_t off = (size_t)r * dim;
+        QINGMING_CUDA_LAUNCH(rt::talker_add_postnorm_fused_kernel, dim3(1), dim3(256), (size_t)dim * 2, (cudaStream_t) nullptr,
+                             dh.as<uint16_t>() + off, da.as<uint16_t>() + off, dw.as<uint16_t>(), dr.as<uint16_t>() + off,
+                             dn.as<uint16_t>() + off, dim, 1.0e-6f);
+        RH_CHECK(cudaGetLastError());
+    }
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(residual, dr.p, bytes, cudaMemcpyDeviceToHost));
+    RH_CHECK(cudaMemcpy(normalized, dn.p, bytes, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int qmref_gate_up_swiglu_rows(const uint16_t* x, const uint16_t* gate_w, const uint16_t* up_w, uint16_t* out, int rows,
+                              int hidden, int intermediate) {
+    DevBuf dx, dg, du, dout;
+    RH_CHECK(dx.alloc((size_t)rows * hidden * 2)); RH_CHECK(dg.alloc((size_t)intermediate * hidden * 2));
+    RH_CHECK(du.alloc((size_t)intermediate * hidden * 2)); RH_CHECK(dout.alloc((size_t)rows * intermediate * 2));
+    RH_CHECK(cudaMemcpy(dx.p, x, dx.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dg.p, gate_w, dg.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(du.p, up_w, du.bytes, cudaMemcpyHostToDevice));
+    for (int r = 0; r < rows; ++r) {
+        QINGMING_CUDA_LAUNCH(rt::talker_gate_up_swiglu_fused_kernel, dim3((unsigned)((intermediate + 15) / 16)), dim3(256),
+                             (size_t)hidden * 2, (cudaStream_t) nullptr, dx.as<uint16_t>() + (size_t)r * hidden, dg.as<uint16_t>(),
+                             du.as<uint16_t>(), dout.as<uint16_t>() + (size_t)r * intermediate, hidden, intermediate);
+        RH_CHECK(cudaGetLastError());
+    }
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(out, dout.p, dout.bytes, cudaMemcpyDeviceToHost));
     return 0;
 }
 

@@ -74,6 +74,10 @@ ABI = {
     "qm_decode_attention_partial": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
                                               c_int32, c_void_p, c_void_p, c_int64, c_void_p]),
     "qm_attention_combine": (c_int32, [c_void_p, c_int32, c_int32, c_void_p, c_void_p]),
+    "qm_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_float, c_void_p]),
+    "qm_add_postnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_float, c_void_p]),
+    "qm_linear": (c_int32, [c_void_p] * 6 + [c_int32, c_int32, c_int32, c_void_p]),
+    "qm_gate_up_swiglu": (c_int32, [c_void_p] * 5 + [c_int32, c_int32, c_int32, c_void_p]),
     "qm_prefill_attention_varlen": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
                                               c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
 }
@@ -258,6 +262,41 @@ class TalkerAttention:
             self.pool, layer, _ptr(q), _ptr(k), _ptr(v), _ptr(q_norm_weight), _ptr(k_norm_weight), _ptr(self.rope_cos),
             _ptr(self.rope_sin), self.max_positions, _ptr(positions), _ptr(page_table), page_table.shape[1], batch,
             self.q_heads, self.epsilon, _ptr(out), _ptr(ws), ws.numel(), _stream()))
+        return out
+
+    # -- rest of the decoder layer (reference launcher names) ----------------
+    def launch_rmsnorm(self, x, weight, out=None):
+        import torch
+
+        out = torch.empty_like(x) if out is None else out
+        _check(self.lib.qm_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), x.shape[0], x.shape[1], self.epsilon, _stream()))
+        return out
+
+    def launch_add_postnorm_m1(self, hidden, attention, weight, residual=None, normalized=None):
+        import torch
+
+        residual = torch.empty_like(hidden) if residual is None else residual
+        normalized = torch.empty_like(hidden) if normalized is None else normalized
+        _check(self.lib.qm_add_postnorm(_ptr(hidden), _ptr(attention), _ptr(weight), _ptr(residual), _ptr(normalized),
+                                        hidden.shape[0], hidden.shape[1], self.epsilon, _stream()))
+        return residual, normalized
+
+    def launch_linear_m1(self, x, weight, bias=None, residual=None, out=None):
+        import torch
+
+        if out is None:
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16, device="cuda")
+        _check(self.lib.qm_linear(self.pool, _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), x.shape[0],
+                                  weight.shape[0], weight.shape[1], _stream()))
+        return out
+
+    def launch_gate_up_swiglu_m1(self, x, gate_weight, up_weight, out=None):
+        import torch
+
+        if out is None:
+            out = torch.empty((x.shape[0], gate_weight.shape[0]), dtype=torch.bfloat16, device="cuda")
+        _check(self.lib.qm_gate_up_swiglu(self.pool, _ptr(x), _ptr(gate_weight), _ptr(up_weight), _ptr(out), x.shape[0],
+                                          x.shape[1], gate_weight.shape[0], _stream()))
         return out
 
     def launch_attention_static(self, layer, q_rot, seq_lens, page_table, out=None):

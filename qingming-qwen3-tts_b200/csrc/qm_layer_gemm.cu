@@ -1,0 +1,355 @@
+// Skinny GEMM for the talker layer's projections at decode time: out[M][N] = x[M][K] * W[N][K]^T with M <= 64 token
+// rows, i.e. pure weight streaming (every weight byte is read once, 2*M flop per byte pair).
+//
+// Stands in for the reference's M = 1 GEMV kernels, which it launches once per token:
+//   talker_linear_fused_kernel           17.cu:15250-15317 (launcher :17646)   o-proj, down-proj (+ residual)
+//   talker_qkv_fused_kernel              17.cu:15321-15407 (launcher :17691)   q, k, v projections
+//   talker_gate_up_swiglu_fused_kernel   17.cu:16348-16416 (launcher :18020)   gate / up projections + SwiGLU
+// and keeps their bf16 materialisation points (projection result, residual sum, gate, up, activation, product).
+//
+// Mapping: the WEIGHT tile is the tensor core's M operand (128 weight rows per CTA), the token rows are its N
+// operand (padded to 32 or 64), so D^T[128 x M] accumulates in 32 / 64 TMEM columns.  K is split across the CTAs
+// of a thread-block cluster; each CTA streams its K range through a TMA ring (128B-swizzled 64-column chunks)
+// and tcgen05.mma; partial sums meet in distributed shared memory and are folded in cluster-rank order, so the
+// result does not depend on timing.  The weight chunks of the first ring stages are requested BEFORE the
+// programmatic-dependent-launch wait: weights are constants, so they can stream in while the previous kernel of
+// the layer is still finishing; only the activations wait.
+#include <new>
+
+#include "qm_tcgen05.cuh"
+
+namespace {
+
+constexpr int kGemmThreads = 192;      // warps 0-3 epilogue (one TMEM lane each), warp 4 MMA issue, warp 5 TMA
+constexpr int kTileRows = 128;         // weight rows per CTA
+constexpr int kChunkCols = 64;         // K columns per ring stage (128 bytes: one swizzle atom)
+constexpr int kWeightStageBytes = kTileRows * kChunkCols * 2;   // 16 KB
+
+enum { EPI_LINEAR = 0, EPI_SWIGLU = 1 };
+
+struct GemmArgs {
+    const uint16_t* bias;        // [N] or null
+    const uint16_t* residual;    // [M][N] or null
+    uint16_t* out;               // [M][N]  (SwiGLU: N = intermediate)
+    uint32_t* status;
+    int rows;                    // M
+    int out_cols;                // N
+    int chunks;                  // K / 64
+    int split;                   // cluster size: CTAs sharing one tile's K range
+};
+
+template <int kMPad>
+struct GemmSmem {
+    static constexpr int kStages = kMPad == 32 ? 4 : 3;
+    static constexpr int kActStageBytes = kMPad * kChunkCols * 2;
+    static constexpr int kStageBytes = kWeightStageBytes + kActStageBytes;
+    static constexpr int kRing = 0;
+    static constexpr int kReduce = kStages * kStageBytes;                 // float[kMPad][128]
+    static constexpr int kBars = kReduce + kMPad * kTileRows * 4;         // full[kStages], empty[kStages], acc
+    static constexpr int kTmemSlot = kBars + (2 * kStages + 1) * 8;
+    static constexpr int kTotal = kTmemSlot + 16;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <int kMPad, int kEpilogue>
+__global__ void __launch_bounds__(kGemmThreads)
+qm_skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap w2_map,
+                      const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
+    using L = GemmSmem<kMPad>;
+    pdl_trigger();
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw_addr = smem_addr(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    unsigned char* smem = smem_raw + pad;
+    const uint32_t sbase = raw_addr + pad;
+    const uint32_t bar0 = sbase + L::kBars;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (L::kStages + s); };
+    const uint32_t acc_bar = bar0 + 8u * (2 * L::kStages);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
+    float* reduce = reinterpret_cast<float*>(smem + L::kReduce);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_rank();
+    const int tile = blockIdx.x / a.split;
+    // this CTA's share of the K chunks (contiguous, sizes differ by at most one)
+    const int chunk_begin = (int)((long long)a.chunks * rank / a.split);
+    const int chunk_end = (int)((long long)a.chunks * (rank + 1) / a.split);
+    const int n_chunks = chunk_end - chunk_begin;
+
+    if (tid == 0) {
+        for (int s = 0; s < L::kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(acc_bar, 1);
+        fence_mbar_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_addr(tmem_slot), kMPad);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    bool dead = false;
+
+    if (warp == 5) {
+        // ------------------------------------------------------------------ TMA
+        if (lane == 0) {
+            auto load_weights = [&](int i) {
+                const int st = i % L::kStages;
+                const uint32_t dst = sbase + L::kRing + st * L::kStageBytes;
+                const int col = (chunk_begin + i) * kChunkCols;
+                mbar_arrive_expect_tx(full_bar(st), L::kStageBytes);
+                if (kEpilogue == EPI_SWIGLU) {
+                    tma_load_2d(dst, &w_map, full_bar(st), col, tile * 64);                 // gate rows -> rows 0..63
+                    tma_load_2d(dst + kWeightStageBytes / 2, &w2_map, full_bar(st), col, tile * 64);   // up rows -> 64..127
+                } else {
+                    tma_load_2d(dst, &w_map, full_bar(st), col, tile * kTileRows);
+                }
+            };
+            auto load_rows = [&](int i) {
+                const int st = i % L::kStages;
+                tma_load_2d(sbase + L::kRing + st * L::kStageBytes + kWeightStageBytes, &x_map, full_bar(st),
+                            (chunk_begin + i) * kChunkCols, 0);
+            };
+            const int head = n_chunks < L::kStages ? n_chunks : L::kStages;
+            for (int i = 0; i < head; ++i) load_weights(i);      // constants: may overlap the previous kernel
+            pdl_wait();                                          // activations come from the previous kernel
+            for (int i = 0; i < head; ++i) load_rows(i);
+            for (int i = head; i < n_chunks; ++i) {
+                const int st = i % L::kStages;
+                if (!mbar_wait_bounded(empty_bar(st), ((i / L::kStages) & 1) ^ 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                load_weights(i);
+                load_rows(i);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 4) {
+        // ------------------------------------------------------------------ MMA
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_instr_desc(kTileRows, kMPad, false);
+            for (int i = 0; i < n_chunks; ++i) {
+                const int st = i % L::kStages;
+                if (!mbar_wait_bounded(full_bar(st), (i / L::kStages) & 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                tc_fence_after();
+                const uint32_t wa = sbase + L::kRing + st * L::kStageBytes;
+                const uint32_t xa = wa + kWeightStageBytes;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    mma_ss(tmem_base, smem_desc(wa + ks * 32, 16, 1024), smem_desc(xa + ks * 32, 16, 1024), idesc,
+                           (i > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(empty_bar(st));
+            }
+            tc_commit(acc_bar);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------- partial sums -> own shared memory
+        if (!mbar_wait_bounded(acc_bar, 0, dead) && lane == 0) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+#pragma unroll
+        for (int c = 0; c < kMPad / 32; ++c) {
+            uint32_t v[32];
+            if (n_chunks > 0) {
+                tmem_ld32(taddr + c * 32, v);
+                tmem_wait_ld();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) reduce[(c * 32 + i) * kTileRows + tid] = __uint_as_float(v[i]);
+        }
+        pdl_wait();      // the stores below may overwrite what the previous kernel still reads
+    }
+
+    // Every CTA of the cluster has its partial tile in shared memory.
+    cluster_sync_all();
+
+    if (warp < 4) {
+        // ------------------------------------------------- fold in rank order + epilogue
+        // Rank r finishes the token rows r, r + split, ...; thread = weight row of the tile.
+        const uint32_t reduce_addr = sbase + L::kReduce;
+        const int active = kEpilogue == EPI_SWIGLU ? 64 : kTileRows;
+        const int col = kEpilogue == EPI_SWIGLU ? tile * 64 + tid : tile * kTileRows + tid;
+        if (tid < active && col < a.out_cols) {
+            for (int m = (int)rank; m < a.rows; m += a.split) {
+                float acc = 0.0f, acc2 = 0.0f;
+                for (int k = 0; k < a.split; ++k) {
+                    acc += ld_cluster_f32(reduce_addr + (uint32_t)(m * kTileRows + tid) * 4u, (uint32_t)k);
+                    if (kEpilogue == EPI_SWIGLU)
+                        acc2 += ld_cluster_f32(reduce_addr + (uint32_t)(m * kTileRows + tid + 64) * 4u, (uint32_t)k);
+                }
+                const size_t o = (size_t)m * a.out_cols + col;
+                if (kEpilogue == EPI_SWIGLU) {
+                    // bf16(gate), bf16(up), bf16(silu(gate)), bf16(product): 17.cu:16396-16404
+                    const float g = round_bf16(acc), u = round_bf16(acc2);
+                    const float act = round_bf16(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))));
+                    a.out[o] = (uint16_t)f32_to_bf16_bits(__fmul_rn(act, u));
+                } else {
+                    // bf16(dot + bias), then bf16(residual + that): 17.cu:15297-15314
+                    if (a.bias) acc = __fadd_rn(acc, bf16_bits_to_f32(a.bias[col]));
+                    uint32_t v = f32_to_bf16_bits(acc);
+                    if (a.residual) v = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(a.residual[o]), bf16_bits_to_f32(v)));
+                    a.out[o] = (uint16_t)v;
+                }
+            }
+        }
+    }
+
+    // Nobody leaves while a peer may still read its shared memory.
+    cluster_sync_all();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kMPad);
+    }
+}
+
+// ---- host side ----------------------------------------------------------------
+
+// [rows][cols] bf16 row-major viewed as {cols, rows}; boxes of box_rows x 64 columns, 128-byte swizzle.
+int32_t encode_matrix_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return qm_fail(QM_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {kChunkCols, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return qm_fail(QM_ECUDA, "cuTensorMapEncodeTiled failed for a projection operand");
+    return QM_OK;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_cluster(void (*kernel)(KArgs...), unsigned grid, unsigned cluster, size_t smem, cudaStream_t stream,
+                           Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = qm_pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+int sm_count_of_current_device() {
+    static thread_local int cached_device = -1, cached_count = 0;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 148;
+    if (device != cached_device) {
+        cudaDeviceProp prop;
+        if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return 148;
+        cached_device = device;
+        cached_count = prop.multiProcessorCount;
+    }
+    return cached_count;
+}
+
+// Cluster size (K split): enough CTAs to occupy every SM about twice, at most 8, at most one chunk each.
+int choose_split(int tiles, int chunks) {
+    const int target = 2 * sm_count_of_current_device();
+    int split = target / (tiles > 0 ? tiles : 1);
+    if (split < 1) split = 1;
+    if (split > 8) split = 8;
+    if (split == 3 || split == 5 || split == 6 || split == 7) split = split >= 4 ? 4 : 2;   // power-of-two clusters only
+    while (split > 1 && chunks / split < 2) split >>= 1;
+    return split;
+}
+
+template <int kEpilogue>
+int32_t run_gemm(const uint16_t* x, const uint16_t* w, const uint16_t* w2, const uint16_t* bias, const uint16_t* residual,
+                 uint16_t* out, int rows, int out_cols, int k_dim, uint32_t* status, cudaStream_t stream, const char* what) {
+    if (!x || !w || !out || (kEpilogue == EPI_SWIGLU && !w2)) return qm_fail(QM_EINVAL, "null tensor pointer");
+    if (rows < 0 || rows > 64) return qm_fail(QM_ECAPACITY, "projection kernels take at most 64 token rows per call");
+    if (out_cols < 1 || k_dim < kChunkCols || k_dim % kChunkCols != 0)
+        return qm_fail(QM_EINVAL, "reduction width must be a positive multiple of 64");
+    const uintptr_t all = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2);
+    if (all & 15u) return qm_fail(QM_EINVAL, "projection operands must be 16-byte aligned");
+    if (rows == 0) return QM_OK;
+    const int m_pad = rows <= 32 ? 32 : 64;
+    const int rows_per_tile = kEpilogue == EPI_SWIGLU ? 64 : kTileRows;
+    const int tiles = (out_cols + rows_per_tile - 1) / rows_per_tile;
+    CUtensorMap w_map, w2_map, x_map;
+    int32_t rc = encode_matrix_map(&w_map, w, (uint64_t)out_cols, (uint64_t)k_dim, (uint32_t)rows_per_tile);
+    if (rc != QM_OK) return rc;
+    rc = encode_matrix_map(&w2_map, kEpilogue == EPI_SWIGLU ? w2 : w, (uint64_t)out_cols, (uint64_t)k_dim, (uint32_t)rows_per_tile);
+    if (rc != QM_OK) return rc;
+    rc = encode_matrix_map(&x_map, x, (uint64_t)rows, (uint64_t)k_dim, (uint32_t)m_pad);
+    if (rc != QM_OK) return rc;
+    GemmArgs a{};
+    a.bias = bias;
+    a.residual = residual;
+    a.out = out;
+    a.status = status;
+    a.rows = rows;
+    a.out_cols = out_cols;
+    a.chunks = k_dim / kChunkCols;
+    a.split = choose_split(tiles, a.chunks);
+    const unsigned grid = (unsigned)(tiles * a.split);
+    cudaError_t err;
+    if (m_pad == 32) {
+        auto kernel = qm_skinny_gemm_kernel<32, kEpilogue>;
+        const size_t smem = GemmSmem<32>::kTotal + 1024;
+        QM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), what);
+        err = launch_cluster(kernel, grid, (unsigned)a.split, smem, stream, w_map, w2_map, x_map, a);
+    } else {
+        auto kernel = qm_skinny_gemm_kernel<64, kEpilogue>;
+        const size_t smem = GemmSmem<64>::kTotal + 1024;
+        QM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), what);
+        err = launch_cluster(kernel, grid, (unsigned)a.split, smem, stream, w_map, w2_map, x_map, a);
+    }
+    QM_CUDA_TRY(err, what);
+    return QM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t qm_linear(qm_kv_pool* pool, const uint16_t* x, const uint16_t* weight, const uint16_t* bias,
+                  const uint16_t* residual, uint16_t* out, int32_t rows, int32_t out_features, int32_t in_features,
+                  void* stream) {
+    if (!pool) return qm_fail(QM_EINVAL, "pool is null");
+    return run_gemm<EPI_LINEAR>(x, weight, nullptr, bias, residual, out, rows, out_features, in_features, pool->status_dev,
+                                static_cast<cudaStream_t>(stream), "projection launch");
+}
+
+int32_t qm_gate_up_swiglu(qm_kv_pool* pool, const uint16_t* x, const uint16_t* gate_weight, const uint16_t* up_weight,
+                          uint16_t* out, int32_t rows, int32_t hidden, int32_t intermediate, void* stream) {
+    if (!pool) return qm_fail(QM_EINVAL, "pool is null");
+    return run_gemm<EPI_SWIGLU>(x, gate_weight, up_weight, nullptr, nullptr, out, rows, intermediate, hidden,
+                                pool->status_dev, static_cast<cudaStream_t>(stream), "fused gate/up/SwiGLU launch");
+}
+
+}  // extern "C"

@@ -1,0 +1,91 @@
+// Row RMSNorm and fused residual-add + post-attention RMSNorm for a batch of token rows.
+//
+// Stand in for code_predictor::rmsnorm_kernel (17.cu:8295-8357, launcher :8927) and
+// talker_add_postnorm_fused_kernel (17.cu:16258-16343, launcher :17989), which the reference launches for one
+// row at a time.  One 256-thread block per row with the reference's own reduction shape - thread t accumulates
+// columns t, t + 256, ... with fmaf, shuffle-down tree per warp, then the tree over the eight warp sums - and its
+// two bf16 roundings, so the bits equal the reference kernels'.
+#include "qm_common.cuh"
+
+namespace {
+
+constexpr int kNormThreads = 256;
+
+// Value of the reference's block reductions (block_reduce_sum :8266, talker_block_sum :15150) for 256 threads.
+__device__ __forceinline__ float block_sum_reference_order(float value, float* warp_values) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) value += __shfl_down_sync(0xffffffffu, value, offset);
+    if (lane == 0) warp_values[warp] = value;
+    __syncthreads();
+    if (warp == 0) {
+        value = lane < kNormThreads / 32 ? warp_values[lane] : 0.0f;
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) value += __shfl_down_sync(0xffffffffu, value, offset);
+        if (lane == 0) warp_values[0] = value;
+    }
+    __syncthreads();
+    return warp_values[0];
+}
+
+// hidden == nullptr: plain RMSNorm of x.  Otherwise x is the attention branch: residual = bf16(hidden + x) is
+// written out and normalised.
+__global__ void __launch_bounds__(kNormThreads) qm_rmsnorm_rows_kernel(const uint16_t* __restrict__ x,
+                                                                      const uint16_t* __restrict__ hidden,
+                                                                      const uint16_t* __restrict__ weight,
+                                                                      uint16_t* __restrict__ residual,
+                                                                      uint16_t* __restrict__ normalized, int dim,
+                                                                      float epsilon) {
+    extern __shared__ uint16_t row_values[];
+    __shared__ float warp_values[8];
+    pdl_trigger();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * dim;
+    float local = 0.0f;
+    for (int c = threadIdx.x; c < dim; c += kNormThreads) {
+        uint32_t bits = x[base + c];
+        if (hidden) {
+            bits = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(hidden[base + c]), bf16_bits_to_f32(bits)));
+            residual[base + c] = (uint16_t)bits;
+        }
+        row_values[c] = (uint16_t)bits;
+        const float v = bf16_bits_to_f32(bits);
+        local = fmaf(v, v, local);
+    }
+    const float sum = block_sum_reference_order(local, warp_values);
+    const float inverse_rms = rsqrtf(__fadd_rn(__fdiv_rn(sum, (float)dim), epsilon));
+    for (int c = threadIdx.x; c < dim; c += kNormThreads) {
+        const float n = round_bf16(__fmul_rn(bf16_bits_to_f32(row_values[c]), inverse_rms));
+        normalized[base + c] = (uint16_t)f32_to_bf16_bits(__fmul_rn(n, bf16_bits_to_f32(weight[c])));
+    }
+}
+
+int32_t launch_norm(const uint16_t* x, const uint16_t* hidden, const uint16_t* weight, uint16_t* residual,
+                    uint16_t* normalized, int rows, int dim, float epsilon, cudaStream_t stream, const char* what) {
+    if (!x || !weight || !normalized) return qm_fail(QM_EINVAL, "null tensor pointer");
+    if (rows < 0 || dim < 1 || dim > 24 * 1024) return qm_fail(QM_EINVAL, "invalid geometry");
+    if (rows == 0) return QM_OK;
+    QM_CUDA_TRY(qm_launch(qm_rmsnorm_rows_kernel, dim3(rows), dim3(kNormThreads), (size_t)dim * sizeof(uint16_t), stream, x,
+                          hidden, weight, residual, normalized, dim, epsilon),
+                what);
+    return QM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t qm_rmsnorm(const uint16_t* x, const uint16_t* weight, uint16_t* out, int32_t rows, int32_t dim, float epsilon,
+                   void* stream) {
+    return launch_norm(x, nullptr, weight, nullptr, out, rows, dim, epsilon, static_cast<cudaStream_t>(stream),
+                       "RMSNorm launch");
+}
+
+int32_t qm_add_postnorm(const uint16_t* hidden, const uint16_t* attention, const uint16_t* weight, uint16_t* residual,
+                        uint16_t* normalized, int32_t rows, int32_t dim, float epsilon, void* stream) {
+    if (!hidden || !residual) return qm_fail(QM_EINVAL, "null tensor pointer");
+    return launch_norm(attention, hidden, weight, residual, normalized, rows, dim, epsilon,
+                       static_cast<cudaStream_t>(stream), "add/postnorm launch");
+}
+
+}  // extern "C"
