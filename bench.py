@@ -482,11 +482,12 @@ def run_prefill_section(pkg, steps, warmup, n_seqs=8):
 def run_talker_step_section(pkg, steps):
     """Secondary measurement: one greedy decode step of a random-init Qwen3 decoder in the 1.7B talker shape
     (28 layers, hidden 2048, 16 q / 8 kv heads, head_dim 128, SwiGLU 6144, RMSNorm, QK-norm, RoPE 1e6, codec vocab
-    3072), 32 streams per GPU at context 2048.  The attention path of every layer is qm_decode_step; everything
-    else (projections, MLP, norms, head, argmax) is plain library code (torch / cuBLAS) that only exists to put the
-    attention path into a whole step - it is not part of the product.  The step is captured in one CUDA graph."""
+    3072), 32 streams per GPU at context 2048, weights ~ N(0, 0.02).  Every layer runs through this library's
+    entry points in the reference's decode_device order (17.cu:17247-17397): RMSNorm, fused QKV projection,
+    qm_decode_step, o-projection, add + post-norm, gate/up SwiGLU, down-projection + residual; then the final norm
+    and the codec head projection.  Only the token embedding gather and the greedy argmax are torch ops.  The
+    step is captured in one CUDA graph."""
     import torch
-    import torch.nn.functional as F
 
     hidden, inter, vocab, layers, streams, context = 2048, 6144, 3072, 28, 32, 2048
     gen = torch.Generator(device="cuda")
@@ -495,13 +496,15 @@ def run_talker_step_section(pkg, steps):
     def weight(*shape):
         return (torch.randn(*shape, generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
 
-    w_qkv = [weight((Q_HEADS + 2 * KV_HEADS) * D, hidden) for _ in range(layers)]
-    w_o = [weight(hidden, Q_HEADS * D) for _ in range(layers)]
-    w_gate_up = [weight(2 * inter, hidden) for _ in range(layers)]
+    nq, nk = Q_HEADS * D, KV_HEADS * D
+    w_q = [weight(nq, hidden) for _ in range(layers)]
+    w_k = [weight(nk, hidden) for _ in range(layers)]
+    w_v = [weight(nk, hidden) for _ in range(layers)]
+    w_o = [weight(hidden, nq) for _ in range(layers)]
+    w_gate = [weight(inter, hidden) for _ in range(layers)]
+    w_up = [weight(inter, hidden) for _ in range(layers)]
     w_down = [weight(hidden, inter) for _ in range(layers)]
-    norm1 = [torch.ones(hidden, dtype=torch.bfloat16, device="cuda") for _ in range(layers)]
-    norm2 = [torch.ones(hidden, dtype=torch.bfloat16, device="cuda") for _ in range(layers)]
-    final_norm = torch.ones(hidden, dtype=torch.bfloat16, device="cuda")
+    norm_w = torch.ones(hidden, dtype=torch.bfloat16, device="cuda")
     head = weight(vocab, hidden)
     embed = weight(vocab, hidden)
     ones = torch.ones(D, dtype=torch.bfloat16, device="cuda")
@@ -518,24 +521,31 @@ def run_talker_step_section(pkg, steps):
     positions = torch.full((streams,), context, dtype=torch.int32, device="cuda")
     tokens = torch.randint(0, vocab, (streams,), generator=gen, device="cuda")
     eng.workspace(streams)
-    attn_out = torch.empty((streams, Q_HEADS, D), dtype=torch.bfloat16, device="cuda")
-    nq, nk = Q_HEADS * D, KV_HEADS * D
+
+    def buf(cols):
+        return torch.empty((streams, cols), dtype=torch.bfloat16, device="cuda")
+
+    x_a, x_b, normed, attn_proj, residual, post, act = buf(hidden), buf(hidden), buf(hidden), buf(hidden), buf(hidden), buf(hidden), buf(inter)
+    q, k, v = buf(nq), buf(nk), buf(nk)
+    context_out = torch.zeros((streams, Q_HEADS, D), dtype=torch.bfloat16, device="cuda")
+    logits = buf(vocab)
 
     def one_step(with_attention=True):
-        x = embed[tokens]
+        cur, nxt = x_a, x_b
+        cur.copy_(embed[tokens])
         for layer in range(layers):
-            h = F.rms_norm(x, (hidden,), norm1[layer], 1e-6)
-            qkv = h @ w_qkv[layer].t()
-            q = qkv[:, :nq].contiguous().view(streams, Q_HEADS, D)
-            k = qkv[:, nq:nq + nk].contiguous().view(streams, KV_HEADS, D)
-            v = qkv[:, nq + nk:].contiguous().view(streams, KV_HEADS, D)
+            eng.launch_rmsnorm(cur, norm_w, out=normed)
+            eng.launch_qkv_m1(normed, w_q[layer], w_k[layer], w_v[layer], out=(q, k, v))
             if with_attention:
-                eng.decode_step(layer, q, k, v, ones, ones, positions, page_table, out=attn_out)
-            x = x + attn_out.view(streams, nq) @ w_o[layer].t()
-            h = F.rms_norm(x, (hidden,), norm2[layer], 1e-6)
-            gu = h @ w_gate_up[layer].t()
-            x = x + (F.silu(gu[:, :inter]) * gu[:, inter:]) @ w_down[layer].t()
-        logits = F.rms_norm(x, (hidden,), final_norm, 1e-6) @ head.t()
+                eng.decode_step(layer, q.view(streams, Q_HEADS, D), k.view(streams, KV_HEADS, D),
+                                v.view(streams, KV_HEADS, D), ones, ones, positions, page_table, out=context_out)
+            eng.launch_linear_m1(context_out.view(streams, nq), w_o[layer], out=attn_proj)
+            eng.launch_add_postnorm_m1(cur, attn_proj, norm_w, residual=residual, normalized=post)
+            eng.launch_gate_up_swiglu_m1(post, w_gate[layer], w_up[layer], out=act)
+            eng.launch_linear_m1(act, w_down[layer], residual=residual, out=nxt)
+            cur, nxt = nxt, cur
+        eng.launch_rmsnorm(cur, norm_w, out=normed)
+        eng.launch_linear_m1(normed, head, out=logits)
         tokens.copy_(torch.argmax(logits.float(), dim=-1))
         positions.add_(1)
 
@@ -573,16 +583,18 @@ def run_talker_step_section(pkg, steps):
     status = eng.status()
     eng.close()
     kv_bytes = layers * streams * (context + 1) * 4096
-    weight_bytes = 2 * (layers * ((Q_HEADS + 2 * KV_HEADS) * D * hidden + hidden * Q_HEADS * D + 3 * inter * hidden) + vocab * hidden)
+    weight_bytes = 2 * (layers * ((nq + 2 * nk) * hidden + hidden * nq + 3 * inter * hidden) + vocab * hidden)
     peak, _ = load_peaks()
     return {"workload": "talker_decode_step_1p7b_shape", "streams_per_gpu": streams, "context": context,
             "ms_per_step": full_ms, "tokens_per_s": streams / (full_ms * 1e-3),
             "attention_ms": full_ms - rest_ms, "attention_share": (full_ms - rest_ms) / full_ms,
-            "non_attention_ms_library_ops": rest_ms, "kv_bytes_per_step": kv_bytes, "weight_bytes_per_step": weight_bytes,
+            "non_attention_ms": rest_ms, "kv_bytes_per_step": kv_bytes, "weight_bytes_per_step": weight_bytes,
+            "weights_gbs": weight_bytes / (rest_ms * 1e-3) / 1e9,
             "hbm_bound_ms": (kv_bytes + weight_bytes) / (peak * 1e9) * 1e3, "device_status": status,
-            "note": "attention = qm_decode_step; projections, MLP, norms, head and argmax are torch/cuBLAS library "
-                    "ops; whole step replayed as one CUDA graph; attention_ms = step with minus step without the "
-                    "attention launches"}
+            "kernel_launches_per_step": layers * 7 + 2,
+            "note": "every layer operator is this library's (norms, tcgen05 projections, fused decode step); the "
+                    "embedding gather and the greedy argmax are torch ops; whole step replayed as one CUDA graph; "
+                    "attention_ms = step with minus step without the qm_decode_step launches"}
 
 
 def run_long_context_section(pkg, world, rank, steps):
@@ -687,6 +699,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the secondary prefill measurement")
     ap.add_argument("--only-prefill", action="store_true", help="run only the prefill section (profiling aid)")
     ap.add_argument("--prefill-seqs", type=int, default=8, help="with --only-prefill: use the first N prompts")
+    ap.add_argument("--only-talker-step", action="store_true", help="run only the whole-decoder-step section (profiling aid)")
     ap.add_argument("--no-talker-step", action="store_true", help="skip the secondary whole-decoder-step measurement")
     ap.add_argument("--no-long-context", action="store_true", help="skip the secondary split-KV long-context measurement")
     ap.add_argument("--layers", type=int, default=LAYERS,
@@ -702,6 +715,16 @@ def main():
         pkg = entry.load_package()
         pkg.load_library()
         print(json.dumps(run_prefill_section(pkg, args.steps, args.warmup, args.prefill_seqs)))
+        return
+    if args.only_talker_step:
+        import torch
+
+        import __graft_entry__ as entry
+
+        torch.cuda.set_device(0)
+        pkg = entry.load_package()
+        pkg.load_library()
+        print(json.dumps(run_talker_step_section(pkg, args.steps)))
         return
     if args.impl == "reference":
         run_reference_arm(args)

@@ -270,6 +270,14 @@ int32_t qm_linear(qm_kv_pool* pool, const uint16_t* x, const uint16_t* weight, c
                   const uint16_t* residual, uint16_t* out, int32_t rows, int32_t out_features, int32_t in_features,
                   void* stream);
 
+/* launch_qkv_m1 (17.cu:17691; kernel talker_qkv_fused_kernel :15321-15407): the three projections of the
+ * normalised hidden rows in one launch, each with its own weight [dim][hidden], optional bias and output tensor
+ * (q_out [rows][q_dim], k_out / v_out [rows][kv_dim]) - the layouts qm_decode_step takes. */
+int32_t qm_qkv_linear(qm_kv_pool* pool, const uint16_t* x, const uint16_t* q_weight, const uint16_t* q_bias,
+                      const uint16_t* k_weight, const uint16_t* k_bias, const uint16_t* v_weight, const uint16_t* v_bias,
+                      uint16_t* q_out, uint16_t* k_out, uint16_t* v_out, int32_t rows, int32_t hidden, int32_t q_dim,
+                      int32_t kv_dim, void* stream);
+
 /* launch_gate_up_swiglu_m1 (17.cu:18020; kernel :16348-16416):
  * out[r][c] = bf16( bf16(silu(bf16(gate))) * bf16(up) ), gate = dot(x[r], gate_weight[c]), up likewise. */
 int32_t qm_gate_up_swiglu(qm_kv_pool* pool, const uint16_t* x, const uint16_t* gate_weight, const uint16_t* up_weight,

@@ -77,6 +77,7 @@ ABI = {
     "qm_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_float, c_void_p]),
     "qm_add_postnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_float, c_void_p]),
     "qm_linear": (c_int32, [c_void_p] * 6 + [c_int32, c_int32, c_int32, c_void_p]),
+    "qm_qkv_linear": (c_int32, [c_void_p] * 11 + [c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "qm_gate_up_swiglu": (c_int32, [c_void_p] * 5 + [c_int32, c_int32, c_int32, c_void_p]),
     "qm_prefill_attention_varlen": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
                                               c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
@@ -288,6 +289,19 @@ class TalkerAttention:
             out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16, device="cuda")
         _check(self.lib.qm_linear(self.pool, _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), x.shape[0],
                                   weight.shape[0], weight.shape[1], _stream()))
+        return out
+
+    def launch_qkv_m1(self, x, q_weight, k_weight, v_weight, q_bias=None, k_bias=None, v_bias=None, out=None):
+        """q, k, v projections in one launch; returns (q [rows][q_dim], k, v [rows][kv_dim])."""
+        import torch
+
+        rows = x.shape[0]
+        if out is None:
+            out = tuple(torch.empty((rows, w.shape[0]), dtype=torch.bfloat16, device="cuda")
+                        for w in (q_weight, k_weight, v_weight))
+        _check(self.lib.qm_qkv_linear(self.pool, _ptr(x), _ptr(q_weight), _ptr(q_bias), _ptr(k_weight), _ptr(k_bias),
+                                      _ptr(v_weight), _ptr(v_bias), _ptr(out[0]), _ptr(out[1]), _ptr(out[2]), rows,
+                                      x.shape[1], q_weight.shape[0], k_weight.shape[0], _stream()))
         return out
 
     def launch_gate_up_swiglu_m1(self, x, gate_weight, up_weight, out=None):

@@ -14,6 +14,7 @@
 // result does not depend on timing.  The weight chunks of the first ring stages are requested BEFORE the
 // programmatic-dependent-launch wait: weights are constants, so they can stream in while the previous kernel of
 // the layer is still finishing; only the activations wait.
+#include <cstdlib>
 #include <new>
 
 #include "qm_tcgen05.cuh"
@@ -27,13 +28,16 @@ constexpr int kWeightStageBytes = kTileRows * kChunkCols * 2;   // 16 KB
 
 enum { EPI_LINEAR = 0, EPI_SWIGLU = 1 };
 
+// Up to three weight matrices that share the input rows (q, k and v projections) run in one launch; each is a
+// segment with its own output tensor.  A plain linear is one segment.
 struct GemmArgs {
-    const uint16_t* bias;        // [N] or null
-    const uint16_t* residual;    // [M][N] or null
-    uint16_t* out;               // [M][N]  (SwiGLU: N = intermediate)
+    const uint16_t* bias[3];     // [N] or null
+    uint16_t* out[3];            // [M][N]  (SwiGLU: N = intermediate)
+    int out_cols[3];             // N of each segment
+    int first_tile[3];           // tile index where each segment starts
+    const uint16_t* residual;    // [M][N] or null (single-segment calls)
     uint32_t* status;
     int rows;                    // M
-    int out_cols;                // N
     int chunks;                  // K / 64
     int split;                   // cluster size: CTAs sharing one tile's K range
 };
@@ -58,18 +62,26 @@ __device__ __forceinline__ uint32_t cluster_rank() {
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+// Address of `local_addr` in the shared memory of CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+// Not volatile and no memory clobber on purpose: the loads of one fold are independent and should all be in
+// flight together; they sit between two cluster barriers (which are compiler barriers) and read data that is
+// not written in between.
+__device__ __forceinline__ float ld_cluster_f32(uint32_t remote_addr) {
     float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote_addr));
     return v;
 }
 
 template <int kMPad, int kEpilogue>
 __global__ void __launch_bounds__(kGemmThreads)
 qm_skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap w2_map,
-                      const __grid_constant__ CUtensorMap x_map, const GemmArgs a) {
+                      const __grid_constant__ CUtensorMap w3_map, const __grid_constant__ CUtensorMap x_map,
+                      const GemmArgs a) {
     using L = GemmSmem<kMPad>;
     pdl_trigger();
     extern __shared__ unsigned char smem_raw[];
@@ -86,7 +98,10 @@ qm_skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_co
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_rank();
-    const int tile = blockIdx.x / a.split;
+    const int global_tile = blockIdx.x / a.split;
+    const int seg = (kEpilogue == EPI_LINEAR) ? (global_tile >= a.first_tile[2] ? 2 : (global_tile >= a.first_tile[1] ? 1 : 0)) : 0;
+    const int tile = global_tile - a.first_tile[seg];
+    const CUtensorMap* seg_map = seg == 0 ? &w_map : (seg == 1 ? &w2_map : &w3_map);
     // this CTA's share of the K chunks (contiguous, sizes differ by at most one)
     const int chunk_begin = (int)((long long)a.chunks * rank / a.split);
     const int chunk_end = (int)((long long)a.chunks * (rank + 1) / a.split);
@@ -122,7 +137,7 @@ qm_skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_co
                     tma_load_2d(dst, &w_map, full_bar(st), col, tile * 64);                 // gate rows -> rows 0..63
                     tma_load_2d(dst + kWeightStageBytes / 2, &w2_map, full_bar(st), col, tile * 64);   // up rows -> 64..127
                 } else {
-                    tma_load_2d(dst, &w_map, full_bar(st), col, tile * kTileRows);
+                    tma_load_2d(dst, seg_map, full_bar(st), col, tile * kTileRows);
                 }
             };
             auto load_rows = [&](int i) {
@@ -191,26 +206,46 @@ qm_skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_co
         const uint32_t reduce_addr = sbase + L::kReduce;
         const int active = kEpilogue == EPI_SWIGLU ? 64 : kTileRows;
         const int col = kEpilogue == EPI_SWIGLU ? tile * 64 + tid : tile * kTileRows + tid;
-        if (tid < active && col < a.out_cols) {
-            for (int m = (int)rank; m < a.rows; m += a.split) {
-                float acc = 0.0f, acc2 = 0.0f;
-                for (int k = 0; k < a.split; ++k) {
-                    acc += ld_cluster_f32(reduce_addr + (uint32_t)(m * kTileRows + tid) * 4u, (uint32_t)k);
-                    if (kEpilogue == EPI_SWIGLU)
-                        acc2 += ld_cluster_f32(reduce_addr + (uint32_t)(m * kTileRows + tid + 64) * 4u, (uint32_t)k);
+        if (tid < active && col < a.out_cols[seg]) {
+            uint32_t peer[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) peer[k] = map_to_rank(reduce_addr + (uint32_t)tid * 4u, (uint32_t)(k < a.split ? k : 0));
+            constexpr int kBatch = 4;                  // token rows folded together: kBatch * split loads in flight
+            for (int m0 = (int)rank; m0 < a.rows; m0 += kBatch * a.split) {
+                float part[kBatch][8], part2[kBatch][8];
+#pragma unroll
+                for (int b = 0; b < kBatch; ++b) {
+                    const int m = m0 + b * a.split;
+                    const uint32_t off = (uint32_t)((m < a.rows ? m : m0) * kTileRows) * 4u;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        part[b][k] = k < a.split ? ld_cluster_f32(peer[k] + off) : 0.0f;
+                        part2[b][k] = (kEpilogue == EPI_SWIGLU && k < a.split) ? ld_cluster_f32(peer[k] + off + 64u * 4u) : 0.0f;
+                    }
                 }
-                const size_t o = (size_t)m * a.out_cols + col;
-                if (kEpilogue == EPI_SWIGLU) {
-                    // bf16(gate), bf16(up), bf16(silu(gate)), bf16(product): 17.cu:16396-16404
-                    const float g = round_bf16(acc), u = round_bf16(acc2);
-                    const float act = round_bf16(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))));
-                    a.out[o] = (uint16_t)f32_to_bf16_bits(__fmul_rn(act, u));
-                } else {
-                    // bf16(dot + bias), then bf16(residual + that): 17.cu:15297-15314
-                    if (a.bias) acc = __fadd_rn(acc, bf16_bits_to_f32(a.bias[col]));
-                    uint32_t v = f32_to_bf16_bits(acc);
-                    if (a.residual) v = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(a.residual[o]), bf16_bits_to_f32(v)));
-                    a.out[o] = (uint16_t)v;
+#pragma unroll
+                for (int b = 0; b < kBatch; ++b) {
+                    const int m = m0 + b * a.split;
+                    if (m >= a.rows) break;
+                    float acc = 0.0f, acc2 = 0.0f;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {       // cluster-rank order; absent ranks contribute +0
+                        acc += part[b][k];
+                        acc2 += part2[b][k];
+                    }
+                    const size_t o = (size_t)m * a.out_cols[seg] + col;
+                    if (kEpilogue == EPI_SWIGLU) {
+                        // bf16(gate), bf16(up), bf16(silu(gate)), bf16(product): 17.cu:16396-16404
+                        const float g = round_bf16(acc), u = round_bf16(acc2);
+                        const float act = round_bf16(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))));
+                        a.out[0][o] = (uint16_t)f32_to_bf16_bits(__fmul_rn(act, u));
+                    } else {
+                        // bf16(dot + bias), then bf16(residual + that): 17.cu:15297-15314
+                        if (a.bias[seg]) acc = __fadd_rn(acc, bf16_bits_to_f32(a.bias[seg][col]));
+                        uint32_t v = f32_to_bf16_bits(acc);
+                        if (a.residual) v = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(a.residual[o]), bf16_bits_to_f32(v)));
+                        a.out[seg][o] = (uint16_t)v;
+                    }
                 }
             }
         }
@@ -278,6 +313,10 @@ int sm_count_of_current_device() {
 
 // Cluster size (K split): enough CTAs to occupy every SM about twice, at most 8, at most one chunk each.
 int choose_split(int tiles, int chunks) {
+    if (const char* forced = std::getenv("QM_GEMM_SPLIT")) {       // tuning aid
+        const int v = std::atoi(forced);
+        if (v >= 1 && v <= 8 && chunks / v >= 1) return v;
+    }
     const int target = 2 * sm_count_of_current_device();
     int split = target / (tiles > 0 ? tiles : 1);
     if (split < 1) split = 1;
@@ -287,33 +326,51 @@ int choose_split(int tiles, int chunks) {
     return split;
 }
 
+struct Segment {
+    const uint16_t* weight;
+    const uint16_t* bias;
+    uint16_t* out;
+    int out_cols;
+};
+
 template <int kEpilogue>
-int32_t run_gemm(const uint16_t* x, const uint16_t* w, const uint16_t* w2, const uint16_t* bias, const uint16_t* residual,
-                 uint16_t* out, int rows, int out_cols, int k_dim, uint32_t* status, cudaStream_t stream, const char* what) {
-    if (!x || !w || !out || (kEpilogue == EPI_SWIGLU && !w2)) return qm_fail(QM_EINVAL, "null tensor pointer");
+int32_t run_gemm(const uint16_t* x, const Segment* segs, int n_segs, const uint16_t* up_weight, const uint16_t* residual,
+                 int rows, int k_dim, uint32_t* status, cudaStream_t stream, const char* what) {
+    if (!x) return qm_fail(QM_EINVAL, "null tensor pointer");
     if (rows < 0 || rows > 64) return qm_fail(QM_ECAPACITY, "projection kernels take at most 64 token rows per call");
-    if (out_cols < 1 || k_dim < kChunkCols || k_dim % kChunkCols != 0)
+    if (k_dim < kChunkCols || k_dim % kChunkCols != 0)
         return qm_fail(QM_EINVAL, "reduction width must be a positive multiple of 64");
-    const uintptr_t all = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2);
+    uintptr_t all = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(up_weight);
+    for (int i = 0; i < n_segs; ++i) {
+        if (!segs[i].weight || !segs[i].out || segs[i].out_cols < 1) return qm_fail(QM_EINVAL, "null tensor pointer");
+        all |= reinterpret_cast<uintptr_t>(segs[i].weight);
+    }
+    if (kEpilogue == EPI_SWIGLU && !up_weight) return qm_fail(QM_EINVAL, "null tensor pointer");
     if (all & 15u) return qm_fail(QM_EINVAL, "projection operands must be 16-byte aligned");
     if (rows == 0) return QM_OK;
     const int m_pad = rows <= 32 ? 32 : 64;
     const int rows_per_tile = kEpilogue == EPI_SWIGLU ? 64 : kTileRows;
-    const int tiles = (out_cols + rows_per_tile - 1) / rows_per_tile;
-    CUtensorMap w_map, w2_map, x_map;
-    int32_t rc = encode_matrix_map(&w_map, w, (uint64_t)out_cols, (uint64_t)k_dim, (uint32_t)rows_per_tile);
-    if (rc != QM_OK) return rc;
-    rc = encode_matrix_map(&w2_map, kEpilogue == EPI_SWIGLU ? w2 : w, (uint64_t)out_cols, (uint64_t)k_dim, (uint32_t)rows_per_tile);
-    if (rc != QM_OK) return rc;
-    rc = encode_matrix_map(&x_map, x, (uint64_t)rows, (uint64_t)k_dim, (uint32_t)m_pad);
-    if (rc != QM_OK) return rc;
+    CUtensorMap maps[3], x_map;
     GemmArgs a{};
-    a.bias = bias;
+    int tiles = 0;
+    for (int i = 0; i < 3; ++i) {
+        const Segment& sg = segs[i < n_segs ? i : n_segs - 1];
+        const uint16_t* wptr = (kEpilogue == EPI_SWIGLU && i == 1) ? up_weight : sg.weight;
+        int32_t rc = encode_matrix_map(&maps[i], wptr, (uint64_t)sg.out_cols, (uint64_t)k_dim, (uint32_t)rows_per_tile);
+        if (rc != QM_OK) return rc;
+        a.first_tile[i] = i < n_segs ? tiles : 0x7fffffff;
+        if (i < n_segs) {
+            a.bias[i] = sg.bias;
+            a.out[i] = sg.out;
+            a.out_cols[i] = sg.out_cols;
+            tiles += (sg.out_cols + rows_per_tile - 1) / rows_per_tile;
+        }
+    }
+    int32_t rc = encode_matrix_map(&x_map, x, (uint64_t)rows, (uint64_t)k_dim, (uint32_t)m_pad);
+    if (rc != QM_OK) return rc;
     a.residual = residual;
-    a.out = out;
     a.status = status;
     a.rows = rows;
-    a.out_cols = out_cols;
     a.chunks = k_dim / kChunkCols;
     a.split = choose_split(tiles, a.chunks);
     const unsigned grid = (unsigned)(tiles * a.split);
@@ -322,12 +379,12 @@ int32_t run_gemm(const uint16_t* x, const uint16_t* w, const uint16_t* w2, const
         auto kernel = qm_skinny_gemm_kernel<32, kEpilogue>;
         const size_t smem = GemmSmem<32>::kTotal + 1024;
         QM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), what);
-        err = launch_cluster(kernel, grid, (unsigned)a.split, smem, stream, w_map, w2_map, x_map, a);
+        err = launch_cluster(kernel, grid, (unsigned)a.split, smem, stream, maps[0], maps[1], maps[2], x_map, a);
     } else {
         auto kernel = qm_skinny_gemm_kernel<64, kEpilogue>;
         const size_t smem = GemmSmem<64>::kTotal + 1024;
         QM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), what);
-        err = launch_cluster(kernel, grid, (unsigned)a.split, smem, stream, w_map, w2_map, x_map, a);
+        err = launch_cluster(kernel, grid, (unsigned)a.split, smem, stream, maps[0], maps[1], maps[2], x_map, a);
     }
     QM_CUDA_TRY(err, what);
     return QM_OK;
@@ -341,15 +398,27 @@ int32_t qm_linear(qm_kv_pool* pool, const uint16_t* x, const uint16_t* weight, c
                   const uint16_t* residual, uint16_t* out, int32_t rows, int32_t out_features, int32_t in_features,
                   void* stream) {
     if (!pool) return qm_fail(QM_EINVAL, "pool is null");
-    return run_gemm<EPI_LINEAR>(x, weight, nullptr, bias, residual, out, rows, out_features, in_features, pool->status_dev,
+    const Segment seg{weight, bias, out, out_features};
+    return run_gemm<EPI_LINEAR>(x, &seg, 1, nullptr, residual, rows, in_features, pool->status_dev,
                                 static_cast<cudaStream_t>(stream), "projection launch");
+}
+
+int32_t qm_qkv_linear(qm_kv_pool* pool, const uint16_t* x, const uint16_t* q_weight, const uint16_t* q_bias,
+                      const uint16_t* k_weight, const uint16_t* k_bias, const uint16_t* v_weight, const uint16_t* v_bias,
+                      uint16_t* q_out, uint16_t* k_out, uint16_t* v_out, int32_t rows, int32_t hidden, int32_t q_dim,
+                      int32_t kv_dim, void* stream) {
+    if (!pool) return qm_fail(QM_EINVAL, "pool is null");
+    const Segment segs[3] = {{q_weight, q_bias, q_out, q_dim}, {k_weight, k_bias, k_out, kv_dim}, {v_weight, v_bias, v_out, kv_dim}};
+    return run_gemm<EPI_LINEAR>(x, segs, 3, nullptr, nullptr, rows, hidden, pool->status_dev, static_cast<cudaStream_t>(stream),
+                                "fused QKV projection launch");
 }
 
 int32_t qm_gate_up_swiglu(qm_kv_pool* pool, const uint16_t* x, const uint16_t* gate_weight, const uint16_t* up_weight,
                           uint16_t* out, int32_t rows, int32_t hidden, int32_t intermediate, void* stream) {
     if (!pool) return qm_fail(QM_EINVAL, "pool is null");
-    return run_gemm<EPI_SWIGLU>(x, gate_weight, up_weight, nullptr, nullptr, out, rows, intermediate, hidden,
-                                pool->status_dev, static_cast<cudaStream_t>(stream), "fused gate/up/SwiGLU launch");
+    const Segment seg{gate_weight, nullptr, out, intermediate};
+    return run_gemm<EPI_SWIGLU>(x, &seg, 1, up_weight, nullptr, rows, hidden, pool->status_dev,
+                                static_cast<cudaStream_t>(stream), "fused gate/up/SwiGLU launch");
 }
 
 }  // extern "C"

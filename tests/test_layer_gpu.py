@@ -138,3 +138,26 @@ def test_against_reference_kernel_bits(qm, name):
         torch.cuda.synchronize()
     finally:
         eng.close()
+
+
+def test_fused_qkv_projection_writes_three_outputs(qm):
+    import torch
+
+    rows, hidden, q_dim, kv_dim = 32, 2048, 2048, 1024
+    x = oracle.normal_bf16(31, (rows, hidden))
+    wq = oracle.scaled_normal_bf16(32, (q_dim, hidden), 0.02)
+    wk = oracle.scaled_normal_bf16(33, (kv_dim, hidden), 0.02)
+    wv = oracle.scaled_normal_bf16(34, (kv_dim, hidden), 0.02)
+    bk = oracle.scaled_normal_bf16(35, (kv_dim,), 0.1)
+    eng = engine(qm)
+    try:
+        q, k, v = eng.launch_qkv_m1(dev(x), dev(wq), dev(wk), dev(wv), k_bias=dev(bk))
+        torch.cuda.synchronize()
+        assert eng.status() == 0
+        close(scenario._bits(q), oracle.linear(x, wq, mode="f64"))
+        close(scenario._bits(k), oracle.linear(x, wk, bk, mode="f64"))
+        close(scenario._bits(v), oracle.linear(x, wv, mode="f64"))
+        # same bits as three separate projections
+        assert np.array_equal(scenario._bits(q), scenario._bits(eng.launch_linear_m1(dev(x), dev(wq))))
+    finally:
+        eng.close()
