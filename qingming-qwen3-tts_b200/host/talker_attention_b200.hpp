@@ -129,6 +129,33 @@ public:
               "Talker generic fused attention launch");
     }
 
+    // ---- the rest of the decoder layer at decode time (17.cu:17259-17386), `batch` token rows per launch
+    void launch_rmsnorm(const uint16_t* x, const uint16_t* weight, uint16_t* out, int batch, int hidden) {
+        check(qm_rmsnorm(x, weight, out, batch, hidden, 1.0e-6f, stream_), "Talker RMSNorm launch");
+    }
+    void launch_qkv_m1(const uint16_t* normed, const uint16_t* q_w, const uint16_t* q_b, const uint16_t* k_w,
+                       const uint16_t* k_b, const uint16_t* v_w, const uint16_t* v_b, uint16_t* q, uint16_t* k,
+                       uint16_t* v, int batch, int hidden) {
+        check(qm_qkv_linear(pool_, normed, q_w, q_b, k_w, k_b, v_w, v_b, q, k, v, batch, hidden, q_heads_ * QM_HEAD_DIM,
+                            kv_heads_ * QM_HEAD_DIM, stream_),
+              "Qingming fused QKV launch");
+    }
+    void launch_linear_m1(const uint16_t* input, const uint16_t* weight, const uint16_t* bias, const uint16_t* residual,
+                          uint16_t* output, int batch, int output_columns, int reduction_columns) {
+        check(qm_linear(pool_, input, weight, bias, residual, output, batch, output_columns, reduction_columns, stream_),
+              "Qingming M1 linear launch");
+    }
+    void launch_add_postnorm_m1(const uint16_t* hidden_rows, const uint16_t* attention, const uint16_t* norm_weight,
+                                uint16_t* residual, uint16_t* normalized, int batch, int hidden) {
+        check(qm_add_postnorm(hidden_rows, attention, norm_weight, residual, normalized, batch, hidden, 1.0e-6f, stream_),
+              "Qingming add/postnorm launch");
+    }
+    void launch_gate_up_swiglu_m1(const uint16_t* input, const uint16_t* gate_w, const uint16_t* up_w, uint16_t* output,
+                                  int batch, int hidden, int intermediate) {
+        check(qm_gate_up_swiglu(pool_, input, gate_w, up_w, output, batch, hidden, intermediate, stream_),
+              "Qingming fused gate/up/SwiGLU launch");
+    }
+
     // QM_DEVSTAT_* bits raised by kernels since the last call (synchronises the stream).
     uint32_t device_status() {
         uint32_t bits = 0;
