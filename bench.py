@@ -624,38 +624,79 @@ def run_long_context_section(pkg, world, rank, steps):
     out = torch.empty_like(q_rot)
     if world > 1:
         runner = sh.ShardedDecode()
+        try:
+            exchange = sh.PeerExchange(eng, rows_capacity=streams * Q_HEADS)
+        except Exception as exc:       # symmetric memory not available: NCCL path only
+            exchange = None
+            exchange_error = f"{type(exc).__name__}: {exc}"
 
-    def one_layer(layer):
+    def layer_nccl(layer):
+        sh.sharded_decode_attention(eng, runner, layer, q_rot, seq_lens, page_table, out=out)
+
+    def layer_peer(layer):
+        sh.sharded_decode_attention_peer(eng, exchange, layer, q_rot, seq_lens, page_table, out=out)
+
+    def layer_single(layer):
+        eng.launch_attention(layer, q_rot, seq_lens, page_table, out=out)
+
+    def measure(one_layer):
+        # the per-layer host work (two ctypes calls) would otherwise dominate a 20-60 us layer: replay a CUDA graph
+        reps = 4
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(2 * layers):
+                one_layer(i % layers)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
         if world > 1:
-            sh.sharded_decode_attention(eng, runner, layer, q_rot, seq_lens, page_table, out=out)
-        else:
-            eng.launch_attention(layer, q_rot, seq_lens, page_table, out=out)
+            dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(reps * layers):
+                one_layer(i % layers)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        replays = max(steps, 5)
+        start.record()
+        for _ in range(replays):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / (replays * reps * layers)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
 
-    for i in range(8):
-        one_layer(i % layers)
-    torch.cuda.synchronize()
+    extra = {}
+    if world == 1:
+        ms = measure(layer_single)
+    else:
+        nccl_ms = measure(layer_nccl)
+        extra["us_per_layer_nccl_all_gather"] = nccl_ms * 1e3
+        if exchange is not None:
+            ms = measure(layer_peer)
+            extra["exchange"] = "one kernel over peer memory (qm_attention_exchange_combine)"
+        else:
+            ms = nccl_ms
+            extra["exchange"] = "NCCL all-gather + combine kernel (" + exchange_error + ")"
+    status = eng.status()
     if world > 1:
         dist.barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    iters = max(steps, 5) * layers
-    start.record()
-    for i in range(iters):
-        one_layer(i % layers)
-    stop.record()
-    torch.cuda.synchronize()
-    ms = start.elapsed_time(stop) / iters
-    if world > 1:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    status = eng.status()
+        exchange = None
     eng.close()
     total_bytes = streams * length * 4096
     peak, _ = load_peaks()
     return {"workload": "long_context_split_kv_b4_l65536", "streams": streams, "kv_len": length, "gpus": world,
             "us_per_layer": ms * 1e3, "aggregate_gbs": total_bytes / (ms * 1e-3) / 1e9,
             "frac_of_measured_hbm_peak_per_gpu": total_bytes / world / (ms * 1e-3) / 1e9 / peak,
-            "exchange_bytes_per_rank": streams * Q_HEADS * 130 * 4 if world > 1 else 0, "device_status": status}
+            "exchange_bytes_per_rank": streams * Q_HEADS * 130 * 4 if world > 1 else 0, "device_status": status, **extra}
 
 
 def cpu_baseline_and_parity(eng, q_rot0, out0, lengths, table):

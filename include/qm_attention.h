@@ -231,6 +231,20 @@ int32_t qm_decode_attention_partial(qm_kv_pool* pool, int32_t layer, const uint1
  * Parts are folded in index order, so the result does not depend on timing. */
 int32_t qm_attention_combine(const float* partials, int32_t parts, int32_t rows, uint16_t* out, void* stream);
 
+/* Exchange + combine in one kernel over peer memory, for streams whose keys are split across the GPUs of one box.
+ * No counterpart in the reference (single GPU).  Every rank calls it at the same point of its stream with its own
+ * partials (from qm_decode_attention_partial); the kernel stores them into every rank's exchange buffer with plain
+ * peer-to-peer stores, waits - bounded, QM_DEVSTAT_TIMEOUT if a rank never shows up - until all ranks' rows of
+ * this call have arrived in its own buffer, and folds them in rank order into out [rows][128] bf16.
+ *   peer_buffers_dev: DEVICE array of `world` pointers, entry r = rank r's exchange buffer mapped into this
+ *     process (symmetric / IPC memory), each of qm_exchange_buffer_bytes(world, rows_capacity) bytes, zero-filled
+ *     once when allocated and never touched by the host afterwards;
+ *   epoch: 1 for the first call on these buffers, then 2, 3, ... - the same on every rank. */
+int64_t qm_exchange_buffer_bytes(int32_t world, int32_t rows_capacity);
+int32_t qm_attention_exchange_combine(qm_kv_pool* pool, const float* local_partials, void* const* peer_buffers_dev,
+                                      int32_t world, int32_t rank, int32_t rows, int32_t rows_capacity, uint64_t epoch,
+                                      uint16_t* out, void* stream);
+
 /* ---- prefill attention: launch_attention with query_length > 1
  *      (17.cu:17954-17985; kernel talker_attention_kernel :15791-16054) */
 

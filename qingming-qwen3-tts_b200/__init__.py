@@ -79,6 +79,9 @@ ABI = {
     "qm_linear": (c_int32, [c_void_p] * 6 + [c_int32, c_int32, c_int32, c_void_p]),
     "qm_qkv_linear": (c_int32, [c_void_p] * 11 + [c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "qm_gate_up_swiglu": (c_int32, [c_void_p] * 5 + [c_int32, c_int32, c_int32, c_void_p]),
+    "qm_exchange_buffer_bytes": (c_int64, [c_int32, c_int32]),
+    "qm_attention_exchange_combine": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+                                                ctypes.c_uint64, c_void_p, c_void_p]),
     "qm_prefill_attention_varlen": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
                                               c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
 }

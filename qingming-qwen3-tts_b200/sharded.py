@@ -62,3 +62,52 @@ def sharded_decode_attention(engine, sharded: ShardedDecode, layer, q_rot, local
         lambda: engine.launch_attention_partial(layer, q_rot, local_seq_lens, page_table),
         lambda gathered: engine.combine(gathered, out=out),
     )
+
+
+class PeerExchange:
+    """Exchange + combine of the partials in one kernel over peer memory (qm_attention_exchange_combine) instead of
+    an all-gather plus a combine kernel.  The exchange buffers are symmetric memory: every rank allocates one and
+    maps the others' (torch.distributed._symmetric_memory over CUDA IPC / NVLink).  Call `run` at the same point on
+    every rank."""
+
+    def __init__(self, engine, rows_capacity: int, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _check, _ptr, _stream  # noqa: F401
+
+        self.engine = engine
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.rows_capacity = rows_capacity
+        nbytes = engine.lib.qm_exchange_buffer_bytes(self.world, rows_capacity)
+        self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        self.buffer.zero_()
+        self.handle = symm_mem.rendezvous(self.buffer, self.group.group_name)
+        self.peer_ptrs = torch.tensor([int(p) for p in self.handle.buffer_ptrs], dtype=torch.int64, device="cuda")
+        self.epoch = 0
+        torch.cuda.synchronize()
+        dist.barrier(self.group)          # every buffer is zeroed and mapped before the first kernel touches it
+
+    def run(self, partial, out=None):
+        """partial [B][Hq][130] fp32 of this rank -> combined [B][Hq][128] bf16 (same bits on every rank)."""
+        import torch
+
+        from . import HEAD_DIM, _check, _ptr, _stream
+
+        rows = partial.shape[0] * partial.shape[1]
+        if out is None:
+            out = torch.empty((partial.shape[0], partial.shape[1], HEAD_DIM), dtype=torch.bfloat16, device="cuda")
+        self.epoch += 1
+        _check(self.engine.lib.qm_attention_exchange_combine(
+            self.engine.pool, _ptr(partial), _ptr(self.peer_ptrs), self.world, self.rank, rows, self.rows_capacity,
+            self.epoch, _ptr(out), _stream()))
+        return out
+
+
+def sharded_decode_attention_peer(engine, exchange: PeerExchange, layer, q_rot, local_seq_lens, page_table, out=None):
+    """Split-KV kernel over this rank's slice, then the one-kernel peer-memory exchange + combine."""
+    partial = engine.launch_attention_partial(layer, q_rot, local_seq_lens, page_table)
+    return exchange.run(partial, out=out)

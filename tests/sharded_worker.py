@@ -54,6 +54,16 @@ def main():
     sums = [torch.zeros_like(mine) for _ in range(world)]
     dist.all_gather(sums, mine)
     assert all(int(x) == int(sums[0]) for x in sums)
+    # the same step through the one-kernel peer-memory exchange: identical bits, three calls in a row
+    exchange = sh.PeerExchange(eng, rows_capacity=sc.batch * 16)
+    lens_dev = torch.from_numpy(local_lens.astype(np.int32)).cuda()
+    for _ in range(3):
+        out_peer = sh.sharded_decode_attention_peer(eng, exchange, 0, q_rot, lens_dev, table)
+    torch.cuda.synchronize()
+    assert eng.status() == 0
+    assert np.array_equal(scenario._bits(out_peer), bits), "peer-memory exchange differs from all-gather + combine"
+    dist.barrier()
+    del exchange
     eng.close()
     dist.barrier()
     if rank == 0:
