@@ -485,8 +485,9 @@ def run_talker_step_section(pkg, steps):
     3072), 32 streams per GPU at context 2048, weights ~ N(0, 0.02).  Every layer runs through this library's
     entry points in the reference's decode_device order (17.cu:17247-17397): RMSNorm, fused QKV projection,
     qm_decode_step, o-projection, add + post-norm, gate/up SwiGLU, down-projection + residual; then the final norm
-    and the codec head projection.  Only the token embedding gather and the greedy argmax are torch ops.  The
-    step is captured in one CUDA graph."""
+    and the codec head projection; the next code comes from qm_final_head_sample (greedy, with the reference's
+    repetition penalty and token suppression) and its embedding row from qm_embedding_gather.  The step is
+    captured in one CUDA graph."""
     import torch
 
     hidden, inter, vocab, layers, streams, context = 2048, 6144, 3072, 28, 32, 2048
@@ -519,7 +520,7 @@ def run_talker_step_section(pkg, steps):
             view.normal_(generator=gen)
     page_table = torch.randperm(num_pages, generator=gen, device="cuda").to(torch.int32).view(streams, pages_per_stream)
     positions = torch.full((streams,), context, dtype=torch.int32, device="cuda")
-    tokens = torch.randint(0, vocab, (streams,), generator=gen, device="cuda")
+    tokens = torch.randint(0, vocab, (streams,), generator=gen, device="cuda").to(torch.int32)
     eng.workspace(streams)
 
     def buf(cols):
@@ -530,9 +531,13 @@ def run_talker_step_section(pkg, steps):
     context_out = torch.zeros((streams, Q_HEADS, D), dtype=torch.bfloat16, device="cuda")
     logits = buf(vocab)
 
+    history = torch.zeros((streams, 8192), dtype=torch.int32, device="cuda")
+    generation = torch.zeros((streams,), dtype=torch.int32, device="cuda")
+    sample_flags = pkg.QM_SAMPLE_REPETITION | pkg.QM_SAMPLE_SUPPRESS | pkg.QM_SAMPLE_RECORD
+
     def one_step(with_attention=True):
         cur, nxt = x_a, x_b
-        cur.copy_(embed[tokens])
+        eng.embedding_gather(embed, tokens, out=cur)
         for layer in range(layers):
             eng.launch_rmsnorm(cur, norm_w, out=normed)
             eng.launch_qkv_m1(normed, w_q[layer], w_k[layer], w_v[layer], out=(q, k, v))
@@ -546,8 +551,10 @@ def run_talker_step_section(pkg, steps):
             cur, nxt = nxt, cur
         eng.launch_rmsnorm(cur, norm_w, out=normed)
         eng.launch_linear_m1(normed, head, out=logits)
-        tokens.copy_(torch.argmax(logits.float(), dim=-1))
+        # greedy: cast, repetition penalty, token suppression, argmax, record - one launch for all streams
+        eng.final_head_sample(logits, generation, history, flags=sample_flags, top_k=0, codes=tokens)
         positions.add_(1)
+        generation.add_(1)
 
     def capture(with_attention):
         side = torch.cuda.Stream()
@@ -556,17 +563,20 @@ def run_talker_step_section(pkg, steps):
             for _ in range(2):
                 one_step(with_attention)
             positions.fill_(context)
+            generation.zero_()
         torch.cuda.current_stream().wait_stream(side)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             one_step(with_attention)
         positions.fill_(context)
+        generation.zero_()
         return graph
 
     def time_graph(graph, n):
         for _ in range(3):
             graph.replay()
         positions.fill_(context)
+        generation.zero_()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
@@ -575,6 +585,7 @@ def run_talker_step_section(pkg, steps):
         b.record()
         torch.cuda.synchronize()
         positions.fill_(context)
+        generation.zero_()
         return a.elapsed_time(b) / n
 
     n = max(5, min(steps, 30))
@@ -591,10 +602,11 @@ def run_talker_step_section(pkg, steps):
             "non_attention_ms": rest_ms, "kv_bytes_per_step": kv_bytes, "weight_bytes_per_step": weight_bytes,
             "weights_gbs": weight_bytes / (rest_ms * 1e-3) / 1e9,
             "hbm_bound_ms": (kv_bytes + weight_bytes) / (peak * 1e9) * 1e3, "device_status": status,
-            "kernel_launches_per_step": layers * 7 + 2,
-            "note": "every layer operator is this library's (norms, tcgen05 projections, fused decode step); the "
-                    "embedding gather and the greedy argmax are torch ops; whole step replayed as one CUDA graph; "
-                    "attention_ms = step with minus step without the qm_decode_step launches"}
+            "kernel_launches_per_step": layers * 7 + 4,
+            "note": "every operator is this library's: embedding gather, norms, tcgen05 projections, fused decode step, "
+                    "codec head, and the final-head chain (repetition penalty, suppression, greedy argmax, history "
+                    "record) in one launch for all streams; only the two counter increments are torch ops; whole step "
+                    "replayed as one CUDA graph; attention_ms = step with minus step without the qm_decode_step launches"}
 
 
 def run_long_context_section(pkg, world, rank, steps):

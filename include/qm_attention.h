@@ -297,6 +297,32 @@ int32_t qm_qkv_linear(qm_kv_pool* pool, const uint16_t* x, const uint16_t* q_wei
 int32_t qm_gate_up_swiglu(qm_kv_pool* pool, const uint16_t* x, const uint16_t* gate_weight, const uint16_t* up_weight,
                           uint16_t* out, int32_t rows, int32_t hidden, int32_t intermediate, void* stream);
 
+/* ---- the end of a decode step: codec-head logits -> next code, and the embedding rows of the next step ---- */
+
+#define QM_SAMPLE_REPETITION 1   /* repetition penalty 1.05 over the stream's history (17.cu:14063-14099)     */
+#define QM_SAMPLE_SUPPRESS 2     /* EOS forbidden for generation_index < 2, reserved ids forbidden (:14102-14123) */
+#define QM_SAMPLE_RECORD 4       /* history[generation_index] = code (record_sampled_code_kernel, :7668-7689) */
+
+/* NativeFinalHead::run_fast / run_fast_device after the head projection (17.cu:14384-14560), for `batch` streams in
+ * one launch: scores = float(logits) (cast_final_head_logits :14052), then the processors selected by `flags`, then
+ *   top_k <= 0: argmax_final_head (:14126-14176) - highest score, lowest index among equals;
+ *   top_k  > 0: gpu_sample_topk_f32_kernel (:7546-7600) - the top_k best by (score desc, index asc), weights
+ *               exp((score - best) / temperature) in double, one SplitMix64 draw from rng_state[stream].
+ * logits [batch][vocab] bf16, vocab <= 4096; history [batch][history_capacity] int32 holds the codes generated so
+ * far, generation_index[stream] of them; codes_out [batch]; processed_out [batch][vocab] float receives the processed
+ * scores when not NULL (what the reference's FinalHeadTrace keeps).  The reference passes eos_token 2150 and
+ * reserved_begin vocab - 1024.  Everything stays on the device: nothing here synchronises or copies to the host. */
+int32_t qm_final_head_sample(qm_kv_pool* pool, const uint16_t* logits, int32_t batch, int32_t vocab, int32_t* history,
+                             int32_t history_capacity, const int32_t* generation_index, int32_t flags,
+                             int32_t eos_token, int32_t reserved_begin, int32_t top_k, float temperature,
+                             uint64_t* rng_state, int32_t* codes_out, float* processed_out, void* stream);
+
+/* gather_embedding_kernel (17.cu:8875-8893) for a batch of rows: out[r][:] = table[token_ids[r]][:].
+ * table [vocab][hidden] bf16, hidden a multiple of 8; an id outside the table is clamped and reported in the
+ * pool's status word (QM_DEVSTAT_BAD_POS). */
+int32_t qm_embedding_gather(qm_kv_pool* pool, const uint16_t* table, const int32_t* token_ids, int32_t rows,
+                            int32_t vocab, int32_t hidden, uint16_t* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

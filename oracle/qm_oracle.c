@@ -670,3 +670,105 @@ QMO_EXPORT void qmo_gate_up_swiglu(const uint16_t* x, const uint16_t* gate_w, co
         }
     }
 }
+
+/* ---- final head: logits -> next code (:14052-14176, :7546-7600, :7668-7689) ---- */
+
+typedef struct {
+    float score;
+    int token;
+} qmo_candidate;
+
+/* gpu_sampler_better (:7492-7496) as a qsort order: higher score first, lower index among equals. */
+static int candidate_order(const void* pa, const void* pb) {
+    const qmo_candidate* a = (const qmo_candidate*)pa;
+    const qmo_candidate* b = (const qmo_candidate*)pb;
+    if (a->score > b->score) return -1;
+    if (a->score < b->score) return 1;
+    return a->token < b->token ? -1 : (a->token > b->token ? 1 : 0);
+}
+
+/* One stream.  `history` holds the codes generated so far, `generation_index` of them.
+ *   scores = float(bf16 logits)                                              cast_final_head_logits :14052-14061
+ *   flag 1: a token present in the history gets score * 1.05 when negative,
+ *           score * 0x3f73cf3e otherwise                                     repetition_penalty :14063-14099
+ *   flag 2: EOS is -inf while generation_index < 2; ids from reserved_begin
+ *           on, except EOS, are -inf                                         suppress_tokens :14102-14123
+ *   top_k <= 0: highest score, lowest index among equals                     argmax_final_head :14126-14176
+ *   top_k  > 0: best top_k in (score desc, index asc) order, weights
+ *               exp(score / T - best / T) in double, target = u * total with
+ *               u one SplitMix64 draw (>> 11, * 2^-53), cumulative walk      gpu_sample_topk_f32_kernel :7546-7600
+ *   flag 4: history[generation_index] = code                                 record_sampled_code_kernel :7668-7689
+ * Returns the code; `processed` (vocab floats) receives the processed scores when not NULL. */
+QMO_EXPORT int qmo_final_head_sample(const uint16_t* logits, int vocab, int32_t* history, int history_capacity,
+                                     int generation_index, int flags, int eos_token, int reserved_begin, int top_k,
+                                     float temperature, uint64_t* rng_state, float* processed) {
+    float* scores = (float*)malloc((size_t)vocab * sizeof(float));
+    qmo_candidate* all = (qmo_candidate*)malloc((size_t)vocab * sizeof(qmo_candidate));
+    const int count = generation_index < history_capacity ? generation_index : history_capacity;
+    union {
+        uint32_t u;
+        float f;
+    } reciprocal = {0x3f73cf3eu};
+    for (int token = 0; token < vocab; ++token) {
+        float score = bf16_to_f32(logits[token]);
+        if (flags & 1) {
+            int repeated = 0;
+            for (int i = 0; i < count; ++i) {
+                if (history[i] == token) {
+                    repeated = 1;
+                    break;
+                }
+            }
+            if (repeated) score = score < 0.0f ? score * 1.05f : score * reciprocal.f;
+        }
+        if (flags & 2) {
+            if (token == eos_token && generation_index < 2) score = -INFINITY;
+            if (token >= reserved_begin && token != eos_token) score = -INFINITY;
+        }
+        scores[token] = score;
+        if (processed) processed[token] = score;
+    }
+    int code = 0;
+    if (top_k <= 0) {
+        float best = -INFINITY;
+        for (int token = 0; token < vocab; ++token) {
+            if (scores[token] > best) {      /* ascending scan: the first of equal scores stays */
+                best = scores[token];
+                code = token;
+            }
+        }
+    } else {
+        for (int token = 0; token < vocab; ++token) {
+            all[token].score = scores[token];
+            all[token].token = token;
+        }
+        qsort(all, (size_t)vocab, sizeof(qmo_candidate), candidate_order);
+        const int keep = top_k < vocab ? top_k : vocab;
+        const double inv_t = 1.0 / (double)temperature;
+        const double maximum = (double)all[0].score * inv_t;
+        double total = 0.0;
+        for (int i = 0; i < keep; ++i) total += exp((double)all[i].score * inv_t - maximum);
+        code = all[0].token;
+        if (total > 0.0) {
+            uint64_t z = *rng_state + 0x9e3779b97f4a7c15ULL;
+            *rng_state = z;
+            z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ULL;
+            z = (z ^ (z >> 27)) * 0x94d049bb133111ebULL;
+            z ^= z >> 31;
+            const double target = (double)(z >> 11) * (1.0 / 9007199254740992.0) * total;
+            double cumulative = 0.0;
+            code = all[keep - 1].token;
+            for (int i = 0; i < keep; ++i) {
+                cumulative += exp((double)all[i].score * inv_t - maximum);
+                if (target < cumulative) {
+                    code = all[i].token;
+                    break;
+                }
+            }
+        }
+    }
+    if ((flags & 4) && generation_index >= 0 && generation_index < history_capacity) history[generation_index] = code;
+    free(scores);
+    free(all);
+    return code;
+}

@@ -329,3 +329,34 @@ def ref_gate_up_swiglu(x, gate_w, up_w):
                                          c_int(gate_w.shape[0]))
     assert rc == 0, rc
     return out
+
+
+def final_head_sample(logits, history=None, generation_index=0, flags=0, eos_token=2150, reserved_begin=None, top_k=0,
+                      temperature=0.9, rng_state=0):
+    """One stream through the restated final-head chain.  Returns (code, processed scores, new rng state, history)."""
+    logits = _u16(logits)
+    vocab = logits.shape[0]
+    hist = np.zeros(8192, dtype=np.int32) if history is None else np.ascontiguousarray(history, dtype=np.int32).copy()
+    state = ctypes.c_uint64(int(rng_state))
+    processed = np.empty(vocab, dtype=np.float32)
+    fn = lib().qmo_final_head_sample
+    fn.restype = c_int
+    code = fn(_p(logits), c_int(vocab), _p(hist), c_int(hist.shape[0]), c_int(int(generation_index)), c_int(flags),
+              c_int(eos_token), c_int(vocab - 1024 if reserved_begin is None else reserved_begin), c_int(top_k),
+              ctypes.c_float(temperature), ctypes.byref(state), _p(processed))
+    return int(code), processed, int(state.value), hist
+
+
+def ref_final_head(logits, history=None, generation_index=0, flags=0, top_k=0, temperature=0.9, rng_state=0):
+    """The reference's own final-head kernels (vocabulary 3072) on the GPU, one stream."""
+    logits = _u16(logits)
+    assert logits.shape[0] == 3072
+    hist = np.zeros(8192, dtype=np.int32) if history is None else np.ascontiguousarray(history, dtype=np.int32).copy()
+    state = ctypes.c_uint64(int(rng_state))
+    processed = np.empty(3072, dtype=np.float32)
+    code = ctypes.c_int32(0)
+    rc = ref().qmref_final_head(_p(logits), _p(hist), c_int(int(generation_index)), c_int(int(generation_index)), c_int(flags),
+                                c_int(top_k), ctypes.c_float(temperature), ctypes.byref(state), _p(processed),
+                                ctypes.byref(code))
+    assert rc == 0, rc
+    return int(code.value), processed, int(state.value), hist

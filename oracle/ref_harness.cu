@@ -279,6 +279,57 @@ int qmref_gate_up_swiglu_rows(const uint16_t* x, const uint16_t* gate_w, const u
     return 0;
 }
 
+// The reference's final-head chain for one stream, as NativeFinalHead::run_fast strings it together:
+// cast_final_head_logits, repetition_penalty (flag 1), suppress_tokens (flag 2), then argmax_final_head
+// (top_k <= 0) or gpu_sample_topk_f32_kernel, then record_sampled_code_kernel (flag 4).  The vocabulary is the
+// reference's fixed 3072.  processed: 3072 floats out; history updated in place when recording; rng_state in/out.
+int qmref_final_head(const uint16_t* logits, int32_t* history, int history_count, int generation_index, int flags,
+                     int top_k, float temperature, uint64_t* rng_state, float* processed, int32_t* code_out) {
+    namespace rb = qwen3_tts::baseline;
+    constexpr int kVocab = 3072;
+    DevBuf dl, dp, dh, dseen, dcode, drng;
+    RH_CHECK(dl.alloc(kVocab * 2)); RH_CHECK(dp.alloc(kVocab * sizeof(float)));
+    RH_CHECK(dh.alloc(8192 * sizeof(int32_t))); RH_CHECK(dseen.alloc(kVocab)); RH_CHECK(dcode.alloc(sizeof(int32_t)));
+    RH_CHECK(drng.alloc(sizeof(uint64_t)));
+    RH_CHECK(cudaMemcpy(dl.p, logits, kVocab * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemset(dseen.p, 0, kVocab));
+    if (history_count > 0) RH_CHECK(cudaMemcpy(dh.p, history, (size_t)history_count * sizeof(int32_t), cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(drng.p, rng_state, sizeof(uint64_t), cudaMemcpyHostToDevice));
+    const dim3 grid((kVocab + 255) / 256), block(256);
+    QINGMING_CUDA_LAUNCH(rb::cast_final_head_logits, grid, block, 0, (cudaStream_t) nullptr, dl.as<uint16_t>(), dp.as<float>());
+    RH_CHECK(cudaGetLastError());
+    if (flags & 1) {
+        QINGMING_CUDA_LAUNCH(rb::repetition_penalty, grid, block, 0, (cudaStream_t) nullptr, dp.as<float>(),
+                             dh.as<int32_t>(), history_count);
+        RH_CHECK(cudaGetLastError());
+    }
+    if (flags & 2) {
+        QINGMING_CUDA_LAUNCH(rb::suppress_tokens, grid, block, 0, (cudaStream_t) nullptr, dp.as<float>(), generation_index);
+        RH_CHECK(cudaGetLastError());
+    }
+    if (top_k > 0) {
+        QINGMING_CUDA_LAUNCH(rb::gpu_sample_topk_f32_kernel, dim3(1), dim3(rb::kGpuSamplerThreads),
+                             rb::gpu_sampler_shared_bytes(), (cudaStream_t) nullptr, dp.as<float>(), kVocab, top_k,
+                             temperature, drng.as<std::uint64_t>(), dcode.as<int32_t>());
+    } else {
+        QINGMING_CUDA_LAUNCH(rb::argmax_final_head, dim3(1), dim3(256), 0, (cudaStream_t) nullptr, dp.as<float>(),
+                             dcode.as<int32_t>());
+    }
+    RH_CHECK(cudaGetLastError());
+    if (flags & 4) {
+        QINGMING_CUDA_LAUNCH(rb::record_sampled_code_kernel, dim3(1), dim3(1), 0, (cudaStream_t) nullptr, dcode.as<int32_t>(),
+                             dh.as<int32_t>(), dseen.as<std::uint8_t>(), generation_index);
+        RH_CHECK(cudaGetLastError());
+    }
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(processed, dp.p, kVocab * sizeof(float), cudaMemcpyDeviceToHost));
+    RH_CHECK(cudaMemcpy(code_out, dcode.p, sizeof(int32_t), cudaMemcpyDeviceToHost));
+    RH_CHECK(cudaMemcpy(rng_state, drng.p, sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    if (flags & 4) RH_CHECK(cudaMemcpy(history + generation_index, dh.as<int32_t>() + generation_index, sizeof(int32_t),
+                                       cudaMemcpyDeviceToHost));
+    return 0;
+}
+
 // Host RoPE table exactly as the engine builds it.
 int qmref_make_rope(int rows, int start, uint16_t* cosine, uint16_t* sine) {
     auto r = qwen3_tts::baseline::make_talker_rope(rows, start);

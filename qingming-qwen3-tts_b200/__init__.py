@@ -32,6 +32,7 @@ QM_ECUDA = -3
 QM_ETIMEOUT = -4
 QM_ENOMEM = -5
 QM_EDEVICE = -6
+QM_SAMPLE_REPETITION, QM_SAMPLE_SUPPRESS, QM_SAMPLE_RECORD = 1, 2, 4
 
 DEVSTAT_BAD_PAGE = 1
 DEVSTAT_BAD_POS = 2
@@ -79,6 +80,9 @@ ABI = {
     "qm_linear": (c_int32, [c_void_p] * 6 + [c_int32, c_int32, c_int32, c_void_p]),
     "qm_qkv_linear": (c_int32, [c_void_p] * 11 + [c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "qm_gate_up_swiglu": (c_int32, [c_void_p] * 5 + [c_int32, c_int32, c_int32, c_void_p]),
+    "qm_final_head_sample": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_int32, c_void_p, c_int32, c_int32,
+                                       c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "qm_embedding_gather": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
     "qm_exchange_buffer_bytes": (c_int64, [c_int32, c_int32]),
     "qm_attention_exchange_combine": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                                 ctypes.c_uint64, c_void_p, c_void_p]),
@@ -314,6 +318,35 @@ class TalkerAttention:
             out = torch.empty((x.shape[0], gate_weight.shape[0]), dtype=torch.bfloat16, device="cuda")
         _check(self.lib.qm_gate_up_swiglu(self.pool, _ptr(x), _ptr(gate_weight), _ptr(up_weight), _ptr(out), x.shape[0],
                                           x.shape[1], gate_weight.shape[0], _stream()))
+        return out
+
+    def final_head_sample(self, logits, generation_index=None, history=None, flags=0, eos_token=2150,
+                          reserved_begin=None, top_k=0, temperature=0.9, rng_state=None, codes=None, processed=None):
+        """NativeFinalHead::run_fast after the head projection (17.cu:14384-14560) for a batch of streams: cast,
+        repetition penalty, token suppression, then argmax (top_k = 0) or top-k sampling; optionally records the
+        code in the history.  rng_state is an int64 tensor holding each stream's SplitMix64 state."""
+        import torch
+
+        batch, vocab = logits.shape
+        if codes is None:
+            codes = torch.empty((batch,), dtype=torch.int32, device="cuda")
+        if reserved_begin is None:
+            reserved_begin = vocab - 1024
+        capacity = history.shape[1] if history is not None else 0
+        _check(self.lib.qm_final_head_sample(self.pool, _ptr(logits), batch, vocab, _ptr(history), capacity,
+                                             _ptr(generation_index), flags, eos_token, reserved_begin, top_k,
+                                             float(temperature), _ptr(rng_state), _ptr(codes), _ptr(processed), _stream()))
+        return codes
+
+    def embedding_gather(self, table, token_ids, out=None):
+        """gather_embedding_kernel (17.cu:8875) for a batch: out[r] = table[token_ids[r]]."""
+        import torch
+
+        rows = token_ids.shape[0]
+        if out is None:
+            out = torch.empty((rows, table.shape[1]), dtype=torch.bfloat16, device="cuda")
+        _check(self.lib.qm_embedding_gather(self.pool, _ptr(table), _ptr(token_ids), rows, table.shape[0], table.shape[1],
+                                            _ptr(out), _stream()))
         return out
 
     def launch_attention_static(self, layer, q_rot, seq_lens, page_table, out=None):

@@ -26,6 +26,7 @@
 // Scores live in the log2 domain (q is pre-multiplied by scale * log2 e).
 #include <math_constants.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "qm_norm_rope.cuh"
@@ -71,6 +72,7 @@ struct DecodeArgs {
     int max_pages;
     int num_pages;
     int mode;
+    int prefetch_units;      // units per CTA whose tiles are prefetched into L2 before the dependency wait
 };
 
 struct SharedLayout {
@@ -124,6 +126,73 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
             mbar_init(staged_bar(s), 1);
         }
         fence_mbar_init();
+    }
+    // ---- L2 warm-up, before the dependency wait.
+    // A CTA of this launch becomes resident as soon as a CTA of the previous kernel retires, often many
+    // microseconds before the last one does, and would otherwise sit idle in the wait below while HBM runs dry.
+    // It works out its share of the units from whatever seq_lens and the page table hold right now and asks
+    // the L2 to fetch the K and V tiles of its first units.  These values may be stale when the previous
+    // kernel is the one that writes them: they only choose prefetch addresses (page ids clamped into the
+    // pool), nothing computed from them survives the wait, and a wrong guess costs a useless prefetch.
+    if (a.prefetch_units > 0) {
+        for (int s = tid; s < a.batch; s += kDecodeThreads) {
+            int len = a.seq_lens[s] + a.len_offset;
+            len = len < 0 ? 0 : (len > a.max_pages * kPageTokens ? a.max_pages * kPageTokens : len);
+            prefix[s + 1] = ((len + kPageTokens - 1) >> 6) * hkv;
+        }
+        if (tid == 0) prefix[0] = 0;
+        __syncthreads();
+        if (warp == 0) {
+            int carry = 0;
+            for (int base = 0; base < a.batch; base += 32) {
+                const int idx = base + lane;
+                int v = idx < a.batch ? prefix[idx + 1] : 0;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, v, off);
+                    if (lane >= off) v += t;
+                }
+                v += carry;
+                if (idx < a.batch) prefix[idx + 1] = v;
+                carry = __shfl_sync(0xffffffffu, v, 31);
+            }
+        }
+        __syncthreads();
+        if (warp == kProducerWarp) {
+            const long long total = prefix[a.batch];
+            const long long geff = total < (long long)gridDim.x ? total : (long long)gridDim.x;
+            if ((long long)blockIdx.x < geff) {
+                const long long ub = (long long)blockIdx.x * total / geff;
+                const long long ue = (long long)(blockIdx.x + 1) * total / geff;
+                if (lane < a.prefetch_units && ub + lane < ue) {
+                    const int u = (int)(ub + lane);
+                    int lo = 0, hi = a.batch;
+                    while (hi - lo > 1) {
+                        const int mid = (lo + hi) >> 1;
+                        if (prefix[mid] <= u) lo = mid; else hi = mid;
+                    }
+                    const int pages = (prefix[lo + 1] - prefix[lo]) / hkv;
+                    if (pages > 0) {
+                        const int r = u - prefix[lo];
+                        const int head = r / pages;
+                        const int page_idx = r - head * pages;
+                        int len = a.seq_lens[lo] + a.len_offset;
+                        len = len > a.max_pages * kPageTokens ? a.max_pages * kPageTokens : len;
+                        int rows = len - page_idx * kPageTokens;
+                        rows = rows > kPageTokens ? kPageTokens : rows;
+                        int page_id = a.page_table[(size_t)lo * a.max_pages + page_idx];
+                        page_id = page_id < 0 ? 0 : (page_id >= a.num_pages ? a.num_pages - 1 : page_id);
+                        if (rows > 0) {
+                            const size_t tile = ((size_t)page_id * hkv + head) * kTileElems;
+                            const uint32_t bytes = (uint32_t)rows * (kHeadDim * 2);
+                            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.key_pool + tile), "r"(bytes) : "memory");
+                            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.value_pool + tile), "r"(bytes) : "memory");
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();     // the prefix array is rebuilt below from the values that are valid after the wait
     }
     pdl_wait();      // everything below reads what earlier kernels on the stream wrote
 
@@ -591,6 +660,17 @@ struct FusedInputs {
     float epsilon;
 };
 
+// Units per CTA to prefetch into L2 ahead of the dependency wait.  QM_DECODE_PREFETCH_UNITS overrides the
+// default (a tuning aid; 0 switches the warm-up off).
+int decode_prefetch_units() {
+    static const int value = [] {
+        const char* text = getenv("QM_DECODE_PREFETCH_UNITS");
+        int v = text ? atoi(text) : 4;
+        return v < 0 ? 0 : (v > 32 ? 32 : v);
+    }();
+    return value;
+}
+
 int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const int32_t* seq_lens,
                    const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads, uint16_t* out,
                    float* partial_out, void* workspace, int64_t workspace_bytes, cudaStream_t stream, int mode,
@@ -634,6 +714,7 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
     a.max_pages = max_pages;
     a.num_pages = pool->num_pages;
     a.mode = mode;
+    a.prefetch_units = decode_prefetch_units();
     if (fused) {
         a.q_norm_weight = fused->q_norm_weight;
         a.k_norm_weight = fused->k_norm_weight;

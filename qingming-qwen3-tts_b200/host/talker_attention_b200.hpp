@@ -156,6 +156,20 @@ public:
               "Qingming fused gate/up/SwiGLU launch");
     }
 
+    // NativeFinalHead::run_fast_device after the head projection (17.cu:14475-14560) for every stream at once:
+    // cast, repetition penalty, token suppression, greedy argmax (top_k = 0) or top-k sampling, history record.
+    void final_head_sample(const uint16_t* logits, int batch, int vocab, int32_t* history, int history_capacity,
+                           const int32_t* generation_index, int flags, int top_k, float temperature, uint64_t* rng_state,
+                           int32_t* codes, int eos_token = 2150) {
+        check(qm_final_head_sample(pool_, logits, batch, vocab, history, history_capacity, generation_index, flags,
+                                   eos_token, vocab - 1024, top_k, temperature, rng_state, codes, nullptr, stream_),
+              "FinalHead sampling launch");
+    }
+    // gather_embedding_kernel (17.cu:8875) for a batch of rows.
+    void gather_embeddings(const uint16_t* table, const int32_t* token_ids, int rows, int vocab, int hidden, uint16_t* out) {
+        check(qm_embedding_gather(pool_, table, token_ids, rows, vocab, hidden, out, stream_), "embedding gather launch");
+    }
+
     // QM_DEVSTAT_* bits raised by kernels since the last call (synchronises the stream).
     uint32_t device_status() {
         uint32_t bits = 0;
