@@ -113,6 +113,13 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def five_numbers(samples):
+    """min / mean / p50 / p95 / max of a list of samples."""
+    x = np.asarray(samples, dtype=np.float64)
+    return {"min": float(x.min()), "mean": float(x.mean()), "p50": float(np.percentile(x, 50)),
+            "p95": float(np.percentile(x, 95)), "max": float(x.max()), "n": int(x.size)}
+
+
 def load_peaks():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -363,6 +370,7 @@ def run_ours(args):
                    "l2": "each layer reads its own 0.57 GB of KV; inputs larger than the 126 MB L2"},
         "us_per_layer": ms_per_step * 1e3 / LAYERS,
         "attention_us_per_layer": attn_ms * 1e3,
+        "launch_us_distribution": five_numbers([x * 1e3 for x in attn_samples]),
         "pct_of_measured_hbm_peak": 100.0 * value / world / peak,
         "pct_of_nominal_8tbs": 100.0 * value / world / 8000.0,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
@@ -393,6 +401,8 @@ def run_ours(args):
         line["prefill"] = prefill
     if not args.no_long_context:
         line["long_context"] = run_long_context_section(pkg, world, rank, args.steps)
+    if not args.no_single_stream and rank == 0:
+        line["single_stream"] = run_single_stream_section(pkg, args.steps)
     if not args.no_talker_step:
         talker = run_talker_step_section(pkg, args.steps)
         if world > 1:
@@ -609,6 +619,68 @@ def run_talker_step_section(pkg, steps):
                     "replayed as one CUDA graph; attention_ms = step with minus step without the qm_decode_step launches"}
 
 
+def run_single_stream_section(pkg, steps):
+    """Secondary measurement: the reference's own operating point - ONE stream, 512 cached tokens (the 0.6B / 1.7B
+    talker attention shape is the same), one new token per step, 28 layers.  2.1 MB of KV per layer, so this is a
+    latency figure: microseconds per layer of the fused decode step, replayed as a CUDA graph of 28 launches and
+    also launched one by one."""
+    import torch
+
+    layers, length = 28, 512
+    pages = (length + 1 + PAGE - 1) // PAGE
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(100)
+    eng = pkg.TalkerAttention(layers=layers, num_pages=pages, q_heads=Q_HEADS, kv_heads=KV_HEADS, max_positions=length + 2)
+    for layer in range(layers):
+        for view in eng.pool_view(layer):
+            view.normal_(generator=gen)
+    table = torch.randperm(pages, generator=gen, device="cuda").to(torch.int32).view(1, pages)
+    positions = torch.full((1,), length, dtype=torch.int32, device="cuda")
+    ones = torch.ones(D, dtype=torch.bfloat16, device="cuda")
+    q = torch.randn(layers, 1, Q_HEADS, D, generator=gen, device="cuda").to(torch.bfloat16)
+    k = torch.randn(layers, 1, KV_HEADS, D, generator=gen, device="cuda").to(torch.bfloat16)
+    v = torch.randn(layers, 1, KV_HEADS, D, generator=gen, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    eng.workspace(1)
+
+    def step():
+        for layer in range(layers):
+            eng.decode_step(layer, q[layer], k[layer], v[layer], ones, ones, positions, table, out=out[layer])
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n / layers * 1e3
+
+    n = max(10, min(steps, 50))
+    graph_us = timed(graph.replay, n)
+    eager_us = timed(step, n)
+    status = eng.status()
+    eng.close()
+    layer_bytes = (length + 1) * 4096 + 12288
+    return {"workload": "single_stream_decode_b1_l512", "kv_len": length, "layers": layers,
+            "us_per_layer_graph": graph_us, "us_per_layer_eager_launches": eager_us,
+            "gbs_graph": layer_bytes / (graph_us * 1e-6) / 1e9, "bytes_per_layer": layer_bytes, "device_status": status,
+            "note": "2.1 MB per layer: launch and memory latency, not bandwidth, set this number"}
+
+
 def run_long_context_section(pkg, world, rank, steps):
     """Secondary measurement: 4 streams of 65 536 keys each, keys split contiguously over the ranks; per layer every
     rank runs the split-KV kernel on its slice, the (m, l, o) partials are all-gathered and combined."""
@@ -755,6 +827,7 @@ def main():
     ap.add_argument("--only-talker-step", action="store_true", help="run only the whole-decoder-step section (profiling aid)")
     ap.add_argument("--no-talker-step", action="store_true", help="skip the secondary whole-decoder-step measurement")
     ap.add_argument("--no-long-context", action="store_true", help="skip the secondary split-KV long-context measurement")
+    ap.add_argument("--no-single-stream", action="store_true", help="skip the secondary one-stream latency measurement")
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="layers per step (default: the talker's 28); a smaller value gives a small case for profiling")
     args = ap.parse_args()
