@@ -403,6 +403,8 @@ def run_ours(args):
         line["long_context"] = run_long_context_section(pkg, world, rank, args.steps)
     if not args.no_single_stream and rank == 0:
         line["single_stream"] = run_single_stream_section(pkg, args.steps)
+    if not args.no_talker_step and rank == 0:
+        line["code_predictor"] = run_code_predictor_section(pkg, args.steps)
     if not args.no_talker_step:
         talker = run_talker_step_section(pkg, args.steps)
         if world > 1:
@@ -681,6 +683,61 @@ def run_single_stream_section(pkg, steps):
             "note": "2.1 MB per layer: launch and memory latency, not bandwidth, set this number"}
 
 
+def run_code_predictor_section(pkg, steps):
+    """Secondary measurement: one frame of the reference's code predictor (15 steps of a 5-layer decoder, hidden
+    1024, same 16 / 8 x 128 attention shape, at most 16 cached positions; 17.cu:13616-13905) for 32 streams, on the
+    same kernels as the talker step, random-init weights in the checkpoint's shapes, greedy, one CUDA graph per
+    frame as in the reference."""
+    import importlib
+
+    import torch
+
+    predictor = importlib.import_module("qingming_qwen3_tts_b200.predictor")
+    streams = 32
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(5000)
+    weights = predictor.random_weights(predictor.PredictorDims(), gen)
+    runner = predictor.CodePredictor(pkg, streams, weights)
+    talker_hidden = torch.randn(streams, predictor.OUTER_HIDDEN, generator=gen, device="cuda").to(torch.bfloat16)
+    first_embedding = torch.randn(streams, predictor.OUTER_HIDDEN, generator=gen, device="cuda").to(torch.bfloat16)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            runner.frame(talker_hidden, first_embedding)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        runner.frame(talker_hidden, first_embedding)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    n = max(5, min(steps, 20))
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(n):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / n
+    status = runner.engine.status()
+    runner.close()
+    d = predictor.PredictorDims()
+    nq, nk = Q_HEADS * D, KV_HEADS * D
+    layer_weights = 2 * ((nq + 2 * nk) * d.hidden + d.hidden * nq + 3 * d.intermediate * d.hidden)
+    token_steps = d.steps + 1
+    weight_bytes = token_steps * (d.layers * layer_weights + 2 * d.hidden * d.outer_hidden) + d.steps * 2 * d.vocab * d.hidden
+    launches = token_steps * (d.layers * 7 + 2) + d.steps * 4
+    peak, _ = load_peaks()
+    return {"workload": "code_predictor_frame_1p7b_shape", "streams_per_gpu": streams, "steps_per_frame": d.steps,
+            "ms_per_frame": ms, "frames_per_s": streams / (ms * 1e-3), "kernel_launches_per_frame": launches,
+            "us_per_launch": ms * 1e3 / launches, "weight_bytes_per_frame": weight_bytes,
+            "hbm_bound_ms": weight_bytes / (peak * 1e9) * 1e3, "device_status": status,
+            "note": "every operator is this library's; 16 token rows per stream and frame through 5 layers; the "
+                    "weights of a layer (29 MB) are small enough to stay in L2 between steps, so launch latency "
+                    "sets the frame time"}
+
+
 def run_long_context_section(pkg, world, rank, steps):
     """Secondary measurement: 4 streams of 65 536 keys each, keys split contiguously over the ranks; per layer every
     rank runs the split-KV kernel on its slice, the (m, l, o) partials are all-gathered and combined."""
@@ -825,6 +882,7 @@ def main():
     ap.add_argument("--only-prefill", action="store_true", help="run only the prefill section (profiling aid)")
     ap.add_argument("--prefill-seqs", type=int, default=8, help="with --only-prefill: use the first N prompts")
     ap.add_argument("--only-talker-step", action="store_true", help="run only the whole-decoder-step section (profiling aid)")
+    ap.add_argument("--only-code-predictor", action="store_true", help="run only the code-predictor frame section (profiling aid)")
     ap.add_argument("--no-talker-step", action="store_true", help="skip the secondary whole-decoder-step measurement")
     ap.add_argument("--no-long-context", action="store_true", help="skip the secondary split-KV long-context measurement")
     ap.add_argument("--no-single-stream", action="store_true", help="skip the secondary one-stream latency measurement")
@@ -850,7 +908,18 @@ def main():
         torch.cuda.set_device(0)
         pkg = entry.load_package()
         pkg.load_library()
-        print(json.dumps(run_talker_step_section(pkg, args.steps)))
+        print(json.dumps({"talker_step": run_talker_step_section(pkg, args.steps),
+                          "code_predictor": run_code_predictor_section(pkg, args.steps)}))
+        return
+    if args.only_code_predictor:
+        import torch
+
+        import __graft_entry__ as entry
+
+        torch.cuda.set_device(0)
+        pkg = entry.load_package()
+        pkg.load_library()
+        print(json.dumps(run_code_predictor_section(pkg, args.steps)))
         return
     if args.impl == "reference":
         run_reference_arm(args)

@@ -21,6 +21,7 @@ reference's ``NativeTalkerEngine`` for this path
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, c_char_p, c_double, c_float, c_int32, c_int64, c_uint32, c_void_p
 
 from ._build import LIB_PATH, build_library
@@ -106,7 +107,7 @@ def load_library(path=None) -> ctypes.CDLL:
     global _lib
     if _lib is not None and path is None:
         return _lib
-    lib_path = str(path or LIB_PATH)
+    lib_path = str(path or os.environ.get("QM_ATTENTION_LIBRARY") or LIB_PATH)     # the variable selects another build of the library
     try:
         lib = ctypes.CDLL(lib_path)
     except OSError as exc:

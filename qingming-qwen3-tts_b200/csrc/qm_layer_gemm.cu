@@ -76,7 +76,6 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t remote_addr) {
     asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote_addr));
     return v;
 }
-
 template <int kMPad, int kEpilogue>
 __global__ void __launch_bounds__(kGemmThreads)
 qm_skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap w2_map,
@@ -107,13 +106,29 @@ qm_skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_co
     const int chunk_end = (int)((long long)a.chunks * (rank + 1) / a.split);
     const int n_chunks = chunk_end - chunk_begin;
 
-    if (tid == 0) {
+    auto load_weights = [&](int i) {
+        const int st = i % L::kStages;
+        const uint32_t dst = sbase + L::kRing + st * L::kStageBytes;
+        const int col = (chunk_begin + i) * kChunkCols;
+        mbar_arrive_expect_tx(full_bar(st), L::kStageBytes);
+        if (kEpilogue == EPI_SWIGLU) {
+            tma_load_2d(dst, &w_map, full_bar(st), col, tile * 64);                 // gate rows -> rows 0..63
+            tma_load_2d(dst + kWeightStageBytes / 2, &w2_map, full_bar(st), col, tile * 64);   // up rows -> 64..127
+        } else {
+            tma_load_2d(dst, seg_map, full_bar(st), col, tile * kTileRows);
+        }
+    };
+    const int head = n_chunks < L::kStages ? n_chunks : L::kStages;
+    if (warp == 5 && lane == 0) {
+        // The copy warp sets up the barriers itself and asks for its first weight chunks right away - weights are
+        // constants, so this may overlap the previous kernel and the TMEM allocation below.
         for (int s = 0; s < L::kStages; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(acc_bar, 1);
         fence_mbar_init();
+        for (int i = 0; i < head; ++i) load_weights(i);
     }
     if (warp == 4) {
         tmem_alloc(smem_addr(tmem_slot), kMPad);
@@ -128,25 +143,11 @@ qm_skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_co
     if (warp == 5) {
         // ------------------------------------------------------------------ TMA
         if (lane == 0) {
-            auto load_weights = [&](int i) {
-                const int st = i % L::kStages;
-                const uint32_t dst = sbase + L::kRing + st * L::kStageBytes;
-                const int col = (chunk_begin + i) * kChunkCols;
-                mbar_arrive_expect_tx(full_bar(st), L::kStageBytes);
-                if (kEpilogue == EPI_SWIGLU) {
-                    tma_load_2d(dst, &w_map, full_bar(st), col, tile * 64);                 // gate rows -> rows 0..63
-                    tma_load_2d(dst + kWeightStageBytes / 2, &w2_map, full_bar(st), col, tile * 64);   // up rows -> 64..127
-                } else {
-                    tma_load_2d(dst, seg_map, full_bar(st), col, tile * kTileRows);
-                }
-            };
             auto load_rows = [&](int i) {
                 const int st = i % L::kStages;
                 tma_load_2d(sbase + L::kRing + st * L::kStageBytes + kWeightStageBytes, &x_map, full_bar(st),
                             (chunk_begin + i) * kChunkCols, 0);
             };
-            const int head = n_chunks < L::kStages ? n_chunks : L::kStages;
-            for (int i = 0; i < head; ++i) load_weights(i);      // constants: may overlap the previous kernel
             pdl_wait();                                          // activations come from the previous kernel
             for (int i = 0; i < head; ++i) load_rows(i);
             for (int i = head; i < n_chunks; ++i) {
