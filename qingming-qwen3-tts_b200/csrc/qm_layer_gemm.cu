@@ -71,10 +71,16 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t ra
 // Not volatile and no memory clobber on purpose: the loads of one fold are independent and should all be in
 // flight together; they sit between two cluster barriers (which are compiler barriers) and read data that is
 // not written in between.
-__device__ __forceinline__ float ld_cluster_f32(uint32_t remote_addr) {
-    float v;
-    asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote_addr));
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t remote_addr) {
+    float4 v;
+    asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote_addr));
     return v;
+}
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
 }
 template <int kMPad, int kEpilogue>
 __global__ void __launch_bounds__(kGemmThreads)
@@ -203,63 +209,74 @@ qm_skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_co
 
     if (warp < 4) {
         // ------------------------------------------------- fold in rank order + epilogue
-        // Rank r finishes the token rows r, r + split, ...; thread = weight row of the tile.
+        // Rank r finishes the token rows r, r + split, ...  One work item = one of those token rows x four
+        // neighbouring weight rows of the tile (one 16-byte read per peer, one 8-byte store); SwiGLU: four gate
+        // rows and the four up rows that go with them.
         const uint32_t reduce_addr = sbase + L::kReduce;
-        const int active = kEpilogue == EPI_SWIGLU ? 64 : kTileRows;
-        const int col = kEpilogue == EPI_SWIGLU ? tile * 64 + tid : tile * kTileRows + tid;
-        if (tid < active && col < a.out_cols[seg]) {
-            uint32_t peer[8];
+        constexpr int kGroups = kEpilogue == EPI_SWIGLU ? 16 : 32;
+        uint32_t peer[8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) peer[k] = map_to_rank(reduce_addr + (uint32_t)tid * 4u, (uint32_t)(k < a.split ? k : 0));
-            constexpr int kBatch = 4;                  // token rows folded together: kBatch * split loads in flight
-            for (int m0 = (int)rank; m0 < a.rows; m0 += kBatch * a.split) {
-                float part[kBatch][8], part2[kBatch][8];
+        for (int k = 0; k < 8; ++k) peer[k] = map_to_rank(reduce_addr, (uint32_t)(k < a.split ? k : 0));
+        const int owned = ((int)rank < a.rows) ? (a.rows - 1 - (int)rank) / a.split + 1 : 0;
+        const int n_cols = a.out_cols[seg];
+        for (int item = tid; item < owned * kGroups; item += 128) {
+            const int g = item % kGroups;
+            const int m = (int)rank + (item / kGroups) * a.split;
+            const uint32_t off = (uint32_t)(m * kTileRows + 4 * g) * 4u;
+            float4 part[8], part2[8];
 #pragma unroll
-                for (int b = 0; b < kBatch; ++b) {
-                    const int m = m0 + b * a.split;
-                    const uint32_t off = (uint32_t)((m < a.rows ? m : m0) * kTileRows) * 4u;
+            for (int k = 0; k < 8; ++k) {
+                part[k] = k < a.split ? ld_cluster_f32x4(peer[k] + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+                part2[k] = (kEpilogue == EPI_SWIGLU && k < a.split) ? ld_cluster_f32x4(peer[k] + off + 64u * 4u)
+                                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        part[b][k] = k < a.split ? ld_cluster_f32(peer[k] + off) : 0.0f;
-                        part2[b][k] = (kEpilogue == EPI_SWIGLU && k < a.split) ? ld_cluster_f32(peer[k] + off + 64u * 4u) : 0.0f;
-                    }
+            for (int k = 0; k < 8; ++k) {       // cluster-rank order; absent ranks contribute +0
+                acc[0] += part[k].x; acc[1] += part[k].y; acc[2] += part[k].z; acc[3] += part[k].w;
+                acc2[0] += part2[k].x; acc2[1] += part2[k].y; acc2[2] += part2[k].z; acc2[3] += part2[k].w;
+            }
+            const int col = (kEpilogue == EPI_SWIGLU ? tile * 64 : tile * kTileRows) + 4 * g;
+            const size_t o = (size_t)m * n_cols + col;
+            uint32_t bits[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (kEpilogue == EPI_SWIGLU) {
+                    // bf16(gate), bf16(up), bf16(silu(gate)), bf16(product): 17.cu:16396-16404
+                    const float gv = round_bf16(acc[i]), u = round_bf16(acc2[i]);
+                    const float act = round_bf16(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))));
+                    bits[i] = f32_to_bf16_bits(__fmul_rn(act, u));
+                } else {
+                    // bf16(dot + bias), then bf16(residual + that): 17.cu:15297-15314
+                    float v = acc[i];
+                    if (a.bias[seg] && col + i < n_cols) v = __fadd_rn(v, bf16_bits_to_f32(a.bias[seg][col + i]));
+                    bits[i] = f32_to_bf16_bits(v);
+                    if (a.residual && col + i < n_cols)
+                        bits[i] = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(a.residual[o + i]), bf16_bits_to_f32(bits[i])));
                 }
+            }
+            uint16_t* dst = (kEpilogue == EPI_SWIGLU ? a.out[0] : a.out[seg]) + o;
+            if (col + 3 < n_cols && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+                *reinterpret_cast<uint2*>(dst) = make_uint2(bits[0] | (bits[1] << 16), bits[2] | (bits[3] << 16));
+            } else {
 #pragma unroll
-                for (int b = 0; b < kBatch; ++b) {
-                    const int m = m0 + b * a.split;
-                    if (m >= a.rows) break;
-                    float acc = 0.0f, acc2 = 0.0f;
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {       // cluster-rank order; absent ranks contribute +0
-                        acc += part[b][k];
-                        acc2 += part2[b][k];
-                    }
-                    const size_t o = (size_t)m * a.out_cols[seg] + col;
-                    if (kEpilogue == EPI_SWIGLU) {
-                        // bf16(gate), bf16(up), bf16(silu(gate)), bf16(product): 17.cu:16396-16404
-                        const float g = round_bf16(acc), u = round_bf16(acc2);
-                        const float act = round_bf16(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))));
-                        a.out[0][o] = (uint16_t)f32_to_bf16_bits(__fmul_rn(act, u));
-                    } else {
-                        // bf16(dot + bias), then bf16(residual + that): 17.cu:15297-15314
-                        if (a.bias[seg]) acc = __fadd_rn(acc, bf16_bits_to_f32(a.bias[seg][col]));
-                        uint32_t v = f32_to_bf16_bits(acc);
-                        if (a.residual) v = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(a.residual[o]), bf16_bits_to_f32(v)));
-                        a.out[seg][o] = (uint16_t)v;
-                    }
-                }
+                for (int i = 0; i < 4; ++i)
+                    if (col + i < n_cols) dst[i] = (uint16_t)bits[i];
             }
         }
     }
 
-    // Nobody leaves while a peer may still read its shared memory.
-    cluster_sync_all();
+    // Nobody leaves while a peer may still read its shared memory.  Only execution order matters here (every
+    // remote read above has returned its value), so the arrival carries no release and does not wait for the
+    // stores above to drain; the matching wait sits at the very end.
+    cluster_arrive_relaxed();
     tc_fence_before();
     __syncthreads();
     if (warp == 4) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kMPad);
     }
+    cluster_wait();
 }
 
 // ---- host side ----------------------------------------------------------------
