@@ -185,8 +185,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                         if (rows > 0) {
                             const size_t tile = ((size_t)page_id * hkv + head) * kTileElems;
                             const uint32_t bytes = (uint32_t)rows * (kHeadDim * 2);
-                            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.key_pool + tile), "r"(bytes) : "memory");
-                            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.value_pool + tile), "r"(bytes) : "memory");
+                            const uint64_t keep = l2_policy_evict_last();
+                            bulk_prefetch_l2_hint(a.key_pool + tile, bytes, keep);
+                            bulk_prefetch_l2_hint(a.value_pool + tile, bytes, keep);
                         }
                     }
                 }
@@ -251,6 +252,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
 
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------ producer
+        const uint64_t stream_once = l2_policy_evict_first();     // a KV tile is read once per step
         for (int base = 0; base < count; base += 32) {
             int seg_l = 0, page_idx_l = 0, pages_l = 1, page_id_l = 0, nvalid_l = 0, head_l = 0;
             if (base + lane < count) {
@@ -300,8 +302,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                         const uint32_t bytes = (uint32_t)nvalid * kRowBytes;
                         mbar_arrive_expect_tx(full_bar(stage), 2 * bytes + (new_segment ? kQBytes : 0u));
                         if (new_segment) bulk_copy_g2s(staging, a.q_rot + (size_t)seg * 2 * kHeadDim, kQBytes, full_bar(stage));
-                        bulk_copy_g2s(dst, a.key_pool + tile, bytes, full_bar(stage));
-                        bulk_copy_g2s(dst + kTileBytes, a.value_pool + tile, bytes, full_bar(stage));
+                        bulk_copy_g2s_hint(dst, a.key_pool + tile, bytes, full_bar(stage), stream_once);
+                        bulk_copy_g2s_hint(dst + kTileBytes, a.value_pool + tile, bytes, full_bar(stage), stream_once);
                     } else {
                         // The last page of a segment ends with the new token, which is not in the pool yet: its
                         // row is built by the consumers from the raw k / v rows staged here.
@@ -328,8 +330,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                         }
                         mbar_arrive_expect_tx(full_bar(stage), 2 * bytes);
                         if (bytes) {
-                            bulk_copy_g2s(dst, a.key_pool + tile, bytes, full_bar(stage));
-                            bulk_copy_g2s(dst + kTileBytes, a.value_pool + tile, bytes, full_bar(stage));
+                            bulk_copy_g2s_hint(dst, a.key_pool + tile, bytes, full_bar(stage), stream_once);
+                            bulk_copy_g2s_hint(dst + kTileBytes, a.value_pool + tile, bytes, full_bar(stage), stream_once);
                         }
                     }
                 }

@@ -112,16 +112,18 @@ qm_skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_co
     const int chunk_end = (int)((long long)a.chunks * (rank + 1) / a.split);
     const int n_chunks = chunk_end - chunk_begin;
 
+    // A weight byte is read once per step: it should not push activations and partial sums out of the L2.
+    const uint64_t weights_once = l2_policy_evict_first();
     auto load_weights = [&](int i) {
         const int st = i % L::kStages;
         const uint32_t dst = sbase + L::kRing + st * L::kStageBytes;
         const int col = (chunk_begin + i) * kChunkCols;
         mbar_arrive_expect_tx(full_bar(st), L::kStageBytes);
         if (kEpilogue == EPI_SWIGLU) {
-            tma_load_2d(dst, &w_map, full_bar(st), col, tile * 64);                 // gate rows -> rows 0..63
-            tma_load_2d(dst + kWeightStageBytes / 2, &w2_map, full_bar(st), col, tile * 64);   // up rows -> 64..127
+            tma_load_2d_hint(dst, &w_map, full_bar(st), col, tile * 64, weights_once);                 // gate rows -> rows 0..63
+            tma_load_2d_hint(dst + kWeightStageBytes / 2, &w2_map, full_bar(st), col, tile * 64, weights_once);   // up rows -> 64..127
         } else {
-            tma_load_2d(dst, seg_map, full_bar(st), col, tile * kTileRows);
+            tma_load_2d_hint(dst, seg_map, full_bar(st), col, tile * kTileRows, weights_once);
         }
     };
     const int head = n_chunks < L::kStages ? n_chunks : L::kStages;
