@@ -40,7 +40,8 @@ constexpr int kProducerWarp = kConsumerWarps;          // issues every bulk copy
 constexpr int kPrepWarp = kConsumerWarps + 1;          // fused step: QK-RMSNorm + RoPE of the staged rows
 constexpr int kDecodeThreads = kConsumerThreads + 64;
 constexpr int kStageBytes = 2 * kTileBytes;
-constexpr int kMaxBatchPerLaunch = 512;
+constexpr int kMaxBatchPerLaunch = 256;        // one stream per thread in the prologue
+static_assert(kMaxBatchPerLaunch <= kDecodeThreads, "the prologue handles one stream per thread");
 constexpr int kMaxGrid = 1024;
 constexpr int kPartialStride = kHeadDim + 2;   // m, l, o[128]
 constexpr float kLog2e = 1.4426950408889634f;
@@ -77,7 +78,8 @@ struct DecodeArgs {
 
 struct SharedLayout {
     static constexpr int kPrefixOff = kStages * kStageBytes;                       // int32[kMaxBatch+1]
-    static constexpr int kScoreOff = kPrefixOff + ((kMaxBatchPerLaunch + 1) * 4 + 15) / 16 * 16;
+    static constexpr int kLenOff = kPrefixOff + ((kMaxBatchPerLaunch + 1) * 4 + 15) / 16 * 16;   // int32[kMaxBatch]: keys per stream
+    static constexpr int kScoreOff = kLenOff + kMaxBatchPerLaunch * 4;
     static constexpr int kMergeOff = kScoreOff + 2 * 2 * kPageTokens * 4;          // float[2][2][64]
     static constexpr int kMergeLOff = kMergeOff + kConsumerWarps * 2 * kHeadDim * 4;
     // per stage: q rows of the two heads (512 B); fused step also cos, sin, raw k, raw v rows (256 B each)
@@ -103,6 +105,7 @@ template <bool kFused>
 __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(const DecodeArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     int32_t* prefix = reinterpret_cast<int32_t*>(smem + SharedLayout::kPrefixOff);
+    int32_t* stream_len = reinterpret_cast<int32_t*>(smem + SharedLayout::kLenOff);
     float* score = reinterpret_cast<float*>(smem + SharedLayout::kScoreOff);
     float* merge_o = reinterpret_cast<float*>(smem + SharedLayout::kMergeOff);
     float* merge_l = reinterpret_cast<float*>(smem + SharedLayout::kMergeLOff);
@@ -127,20 +130,19 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
         }
         fence_mbar_init();
     }
-    // ---- L2 warm-up, before the dependency wait.
+    // ---- Work done before the dependency wait, and kept if it turns out to be right.
     // A CTA of this launch becomes resident as soon as a CTA of the previous kernel retires, often many
     // microseconds before the last one does, and would otherwise sit idle in the wait below while HBM runs dry.
-    // It works out its share of the units from whatever seq_lens and the page table hold right now and asks
-    // the L2 to fetch the K and V tiles of its first units.  These values may be stale when the previous
-    // kernel is the one that writes them: they only choose prefetch addresses (page ids clamped into the
-    // pool), nothing computed from them survives the wait, and a wrong guess costs a useless prefetch.
-    if (a.prefetch_units > 0) {
-        for (int s = tid; s < a.batch; s += kDecodeThreads) {
-            int len = a.seq_lens[s] + a.len_offset;
-            len = len < 0 ? 0 : (len > a.max_pages * kPageTokens ? a.max_pages * kPageTokens : len);
-            prefix[s + 1] = ((len + kPageTokens - 1) >> 6) * hkv;
-        }
-        if (tid == 0) prefix[0] = 0;
+    // It therefore works out the unit partition and the page ids of its first units from whatever seq_lens and
+    // the page table hold right now, and asks the L2 to fetch the K and V tiles of its first units.  These values
+    // may be stale when the previous kernel is the one that writes them, so after the wait every length is read
+    // again and compared (one L2 round trip instead of the whole partition pipeline); the page ids are read
+    // again in any case.  Only if a length changed is the partition rebuilt.  A wrong guess costs a useless
+    // prefetch and nothing else.
+    const int cap_len = a.max_pages * kPageTokens;
+    auto units_of = [&](int len) { return ((len + kPageTokens - 1) >> 6) * hkv; };
+    // prefix[s + 1] holds the units of stream s on entry; on exit prefix[s] = first unit of stream s
+    auto scan_prefix = [&]() {
         __syncthreads();
         if (warp == 0) {
             int carry = 0;
@@ -158,68 +160,84 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
             }
         }
         __syncthreads();
+    };
+    // One unit's coordinates from the partition in shared memory (no global access).
+    struct UnitMeta {
+        int seg, page_idx, pages, nvalid, head, len;
+        long long table_index;       // page_table entry of the unit's page
+    };
+    auto locate = [&](int u) {
+        int lo = 0, hi = a.batch;       // largest s with prefix[s] <= u and units in s
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (prefix[mid] <= u) lo = mid; else hi = mid;
+        }
+        UnitMeta um;
+        const int r = u - prefix[lo];
+        um.pages = (prefix[lo + 1] - prefix[lo]) / hkv;
+        um.head = um.pages > 0 ? r / um.pages : 0;
+        um.page_idx = r - um.head * um.pages;
+        um.seg = lo * hkv + um.head;
+        um.len = stream_len[lo];
+        const int left = um.len - um.page_idx * kPageTokens;
+        um.nvalid = left < kPageTokens ? left : kPageTokens;
+        um.table_index = (long long)lo * a.max_pages + um.page_idx;
+        return um;
+    };
+
+    const bool speculate = a.prefetch_units > 0;
+    UnitMeta first_units{};                      // producer warp: lane l holds this CTA's unit l (speculated)
+    bool first_units_known = false;
+    if (speculate) {
+        if (tid < a.batch) {
+            int len = a.seq_lens[tid] + a.len_offset;
+            len = len < 0 ? 0 : (len > cap_len ? cap_len : len);
+            stream_len[tid] = len;
+            prefix[tid + 1] = units_of(len);
+        }
+        if (tid == 0) prefix[0] = 0;
+        scan_prefix();
         if (warp == kProducerWarp) {
             const long long total = prefix[a.batch];
             const long long geff = total < (long long)gridDim.x ? total : (long long)gridDim.x;
             if ((long long)blockIdx.x < geff) {
                 const long long ub = (long long)blockIdx.x * total / geff;
                 const long long ue = (long long)(blockIdx.x + 1) * total / geff;
-                if (lane < a.prefetch_units && ub + lane < ue) {
-                    const int u = (int)(ub + lane);
-                    int lo = 0, hi = a.batch;
-                    while (hi - lo > 1) {
-                        const int mid = (lo + hi) >> 1;
-                        if (prefix[mid] <= u) lo = mid; else hi = mid;
-                    }
-                    const int pages = (prefix[lo + 1] - prefix[lo]) / hkv;
-                    if (pages > 0) {
-                        const int r = u - prefix[lo];
-                        const int head = r / pages;
-                        const int page_idx = r - head * pages;
-                        int len = a.seq_lens[lo] + a.len_offset;
-                        len = len > a.max_pages * kPageTokens ? a.max_pages * kPageTokens : len;
-                        int rows = len - page_idx * kPageTokens;
-                        rows = rows > kPageTokens ? kPageTokens : rows;
-                        int page_id = a.page_table[(size_t)lo * a.max_pages + page_idx];
+                first_units_known = true;
+                if (ub + lane < ue) {
+                    first_units = locate((int)(ub + lane));
+                    if (lane < a.prefetch_units && first_units.nvalid > 0) {
+                        int page_id = a.page_table[first_units.table_index];
                         page_id = page_id < 0 ? 0 : (page_id >= a.num_pages ? a.num_pages - 1 : page_id);
-                        if (rows > 0) {
-                            const size_t tile = ((size_t)page_id * hkv + head) * kTileElems;
-                            const uint32_t bytes = (uint32_t)rows * (kHeadDim * 2);
-                            const uint64_t keep = l2_policy_evict_last();
-                            bulk_prefetch_l2_hint(a.key_pool + tile, bytes, keep);
-                            bulk_prefetch_l2_hint(a.value_pool + tile, bytes, keep);
-                        }
+                        const size_t tile = ((size_t)page_id * hkv + first_units.head) * kTileElems;
+                        const uint32_t bytes = (uint32_t)first_units.nvalid * (kHeadDim * 2);
+                        const uint64_t keep = l2_policy_evict_last();
+                        bulk_prefetch_l2_hint(a.key_pool + tile, bytes, keep);
+                        bulk_prefetch_l2_hint(a.value_pool + tile, bytes, keep);
                     }
                 }
             }
         }
-        __syncthreads();     // the prefix array is rebuilt below from the values that are valid after the wait
     }
     pdl_wait();      // everything below reads what earlier kernels on the stream wrote
 
-    // Units per stream, then an inclusive scan -> prefix[s] = first unit of stream s.
-    for (int s = tid; s < a.batch; s += kDecodeThreads) {
-        const int len = clamp_len(a.seq_lens[s] + a.len_offset, a.max_pages, a.status);
-        prefix[s + 1] = ((len + kPageTokens - 1) >> 6) * hkv;
+    // The lengths as they are now (one per thread: a launch takes at most kMaxBatchPerLaunch <= blockDim streams).
+    int my_len = 0;
+    bool changed = !speculate;
+    if (tid < a.batch) {
+        my_len = clamp_len(a.seq_lens[tid] + a.len_offset, a.max_pages, a.status);
+        if (speculate && my_len != stream_len[tid]) changed = true;
     }
-    if (tid == 0) prefix[0] = 0;
-    __syncthreads();
-    if (warp == 0) {
-        int carry = 0;
-        for (int base = 0; base < a.batch; base += 32) {
-            const int idx = base + lane;
-            int v = idx < a.batch ? prefix[idx + 1] : 0;
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int t = __shfl_up_sync(0xffffffffu, v, off);
-                if (lane >= off) v += t;
-            }
-            v += carry;
-            if (idx < a.batch) prefix[idx + 1] = v;
-            carry = __shfl_sync(0xffffffffu, v, 31);
+    changed = __syncthreads_or(changed ? 1 : 0) != 0;
+    if (changed) {
+        if (tid < a.batch) {
+            stream_len[tid] = my_len;
+            prefix[tid + 1] = units_of(my_len);
         }
+        if (tid == 0) prefix[0] = 0;
+        scan_prefix();
+        first_units_known = false;
     }
-    __syncthreads();
 
     // Streams with nothing to attend get a zero row (mode 0) or an empty partial (mode 1).
     for (int s = blockIdx.x; s < a.batch; s += gridDim.x) {
@@ -254,24 +272,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
         // ------------------------------------------------------------ producer
         const uint64_t stream_once = l2_policy_evict_first();     // a KV tile is read once per step
         for (int base = 0; base < count; base += 32) {
-            int seg_l = 0, page_idx_l = 0, pages_l = 1, page_id_l = 0, nvalid_l = 0, head_l = 0;
+            int seg_l = 0, page_idx_l = 0, pages_l = 1, page_id_l = 0, nvalid_l = 0, head_l = 0, len_l = 0;
             if (base + lane < count) {
-                const int u = (int)(unit_begin + base + lane);
-                int lo = 0, hi = a.batch;       // largest s with prefix[s] <= u and units in s
-                while (hi - lo > 1) {
-                    const int mid = (lo + hi) >> 1;
-                    if (prefix[mid] <= u) lo = mid; else hi = mid;
-                }
-                const int s = lo;
-                const int r = u - prefix[s];
-                pages_l = (prefix[s + 1] - prefix[s]) / hkv;
-                head_l = r / pages_l;
-                page_idx_l = r - head_l * pages_l;
-                seg_l = s * hkv + head_l;
-                const int len = clamp_len(a.seq_lens[s] + a.len_offset, a.max_pages, a.status);
-                const int left = len - page_idx_l * kPageTokens;
-                nvalid_l = left < kPageTokens ? left : kPageTokens;
-                page_id_l = a.page_table[(size_t)s * a.max_pages + page_idx_l];
+                // the first 32 units were located before the wait; only their page ids are read again
+                const UnitMeta um = (base == 0 && first_units_known) ? first_units : locate((int)(unit_begin + base + lane));
+                seg_l = um.seg;
+                page_idx_l = um.page_idx;
+                pages_l = um.pages;
+                nvalid_l = um.nvalid;
+                head_l = um.head;
+                len_l = um.len;
+                page_id_l = a.page_table[um.table_index];
                 if (page_id_l < 0 || page_id_l >= a.num_pages) {
                     atomicOr(a.status, QM_DEVSTAT_BAD_PAGE);
                     page_id_l = 0;
@@ -285,6 +296,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                 const int page_id = __shfl_sync(0xffffffffu, page_id_l, j);
                 const int nvalid = __shfl_sync(0xffffffffu, nvalid_l, j);
                 const int head = __shfl_sync(0xffffffffu, head_l, j);
+                const int len = __shfl_sync(0xffffffffu, len_l, j);
                 if (lane == 0) {
                     const int n = base + j;
                     const int stage = n % kStages;
@@ -309,8 +321,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                         // row is built by the consumers from the raw k / v rows staged here.
                         const bool last_page = page_idx == pages - 1;
                         const uint32_t bytes = (uint32_t)(last_page ? nvalid - 1 : nvalid) * kRowBytes;
-                        const int stream = seg / hkv;
-                        int position = a.seq_lens[stream];
+                        int position = len - 1;            // fused step: keys = position + 1 (a clamped length is reported)
                         if (position < 0 || position >= a.rope_rows) {
                             atomicOr(a.status, QM_DEVSTAT_BAD_POS);
                             position = position < 0 ? 0 : a.rope_rows - 1;

@@ -173,6 +173,6 @@ def test_reset_request_zeroes_the_pool(qm):
 
 
 def test_batch_larger_than_one_launch_chunk(qm):
-    # more than 512 streams: the host splits the batch into several launches that share the workspace
+    # more streams than one launch takes (256): the host splits the batch into several launches that share the workspace
     lengths = [int(x) for x in oracle.uniform_int(555, 0, 150, 700)]
     check_step(qm, scenario.DecodeScenario(seed=14, lengths=lengths))
