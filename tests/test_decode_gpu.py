@@ -176,3 +176,41 @@ def test_batch_larger_than_one_launch_chunk(qm):
     # more streams than one launch takes (256): the host splits the batch into several launches that share the workspace
     lengths = [int(x) for x in oracle.uniform_int(555, 0, 150, 700)]
     check_step(qm, scenario.DecodeScenario(seed=14, lengths=lengths))
+
+
+def test_lengths_written_by_the_launch_just_before(qm):
+    """The decode kernel works out its unit partition before its dependency wait and keeps it only if the lengths
+    still hold afterwards.  Here the launch immediately before it (qm_embedding_gather, which lets its successor
+    start early) overwrites seq_lens, so the early guess may be made from the OLD lengths; the result must be the
+    one for the NEW lengths, bit for bit the same as when the lengths were in place all along."""
+    import torch
+
+    sc = scenario.DecodeScenario(seed=21, lengths=[300, 17, 129, 64, 1000, 5, 640, 77])
+    b = sc.batch
+    eng = qm.TalkerAttention(layers=1, num_pages=sc.num_pages, q_heads=sc.q_heads, kv_heads=sc.kv_heads, max_positions=sc.max_pos)
+    try:
+        tb = scenario._bf16_tensor
+        kp, vp = sc.pools()
+        kview, vview = eng.pool_view(0)
+        kview.copy_(tb(torch, kp))
+        vview.copy_(tb(torch, vp))
+        page_table = torch.from_numpy(np.maximum(sc.page_table, 0)).cuda()
+        positions = torch.from_numpy(sc.lengths).cuda()
+        q_rot = eng.launch_qk_norm_rope_cache_m1(0, tb(torch, sc.q), tb(torch, sc.k), tb(torch, sc.v), tb(torch, sc.q_w),
+                                                 tb(torch, sc.k_w), positions, page_table)
+        new_lens = torch.from_numpy(sc.lengths + 1).cuda()
+        want = eng.launch_attention(0, q_rot, new_lens, page_table).clone()
+        # the "table" holds two rows of raw bytes: the new lengths and a set of much shorter old ones
+        old_lens = torch.clamp(new_lens // 3, min=1)
+        table = torch.stack([new_lens, old_lens]).view(torch.bfloat16)            # [2][2 * b] bf16
+        seq_lens = torch.empty(b, dtype=torch.int32, device="cuda")
+        rows = torch.tensor([[1], [0]], dtype=torch.int32, device="cuda")
+        for _ in range(20):
+            eng.embedding_gather(table, rows[0], out=seq_lens.view(torch.bfloat16).view(1, 2 * b))   # old lengths
+            torch.cuda.synchronize()
+            eng.embedding_gather(table, rows[1], out=seq_lens.view(torch.bfloat16).view(1, 2 * b))   # new, just in time
+            got = eng.launch_attention(0, q_rot, seq_lens, page_table)
+            assert torch.equal(got, want)
+        assert eng.status() == 0
+    finally:
+        eng.close()
