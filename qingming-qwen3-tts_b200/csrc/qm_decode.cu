@@ -611,15 +611,38 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                     named_bar_sync(1, kConsumerThreads);
                     if (*fold_flag) {
                         __threadfence();
+                        // Piece i of the segment sits in slot (c_first + i + seg).  The loads of a batch are issued
+                        // together (a rolled loop would pay one L2 round trip per piece, twice); the arithmetic stays
+                        // in piece order.
+                        const int pieces = c_last - c_first + 1;
+                        const float* first = a.ws_partials + ((size_t)(c_first + seg) * 2 + qh) * kPartialStride;
+                        constexpr size_t kNext = 2 * kPartialStride;
                         float big = -CUDART_INF_F;
-                        for (int c = c_first; c <= c_last; ++c)
-                            big = fmaxf(big, __ldcg(a.ws_partials + ((size_t)(c + seg) * 2 + qh) * kPartialStride));
+                        for (int i0 = 0; i0 < pieces; i0 += 8) {
+                            float mv[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) mv[j] = i0 + j < pieces ? __ldcg(first + (size_t)(i0 + j) * kNext) : -CUDART_INF_F;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) big = fmaxf(big, mv[j]);
+                        }
                         float acc = 0.0f, denom = 0.0f;
-                        for (int c = c_first; c <= c_last; ++c) {
-                            const float* src = a.ws_partials + ((size_t)(c + seg) * 2 + qh) * kPartialStride;
-                            const float w = fast_exp2(__ldcg(src) - big);
-                            denom = fmaf(w, __ldcg(src + 1), denom);
-                            acc = fmaf(w, __ldcg(src + 2 + d), acc);
+                        for (int i0 = 0; i0 < pieces; i0 += 4) {
+                            float mv[4], lv[4], ov[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float* src = first + (size_t)(i0 + j < pieces ? i0 + j : pieces - 1) * kNext;
+                                mv[j] = __ldcg(src);
+                                lv[j] = __ldcg(src + 1);
+                                ov[j] = __ldcg(src + 2 + d);
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (i0 + j < pieces) {
+                                    const float w = fast_exp2(mv[j] - big);
+                                    denom = fmaf(w, lv[j], denom);
+                                    acc = fmaf(w, ov[j], acc);
+                                }
+                            }
                         }
                         if (a.mode == 0) {
                             a.out[row * kHeadDim + d] = (uint16_t)f32_to_bf16_bits(acc / denom);
