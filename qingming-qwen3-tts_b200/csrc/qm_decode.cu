@@ -662,6 +662,204 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
     }
 }
 
+// ---------------------------------------------------------------------------
+// Short contexts: every stream fits one page (at most 64 keys), e.g. the code predictor's 16 positions or the
+// first steps of a talker request.  The split-KV machinery above (unit partition, ring, partials, fold) is all
+// overhead there; one small CTA per (stream, kv head) does the whole segment: the page's valid rows come in with two
+// bulk copies, four warps score 8 keys per pass (half-warp per key row, as above), one warp per query head does
+// the softmax, and every thread owns two output dimensions of one head.  kFused as above: QK-RMSNorm + RoPE of the
+// raw q rows and of the new token's K row, which is appended to the pool and attended in the same launch.
+constexpr int kShortThreads = 128;
+
+struct ShortSmem {
+    static constexpr int kTile = 0;                               // K rows then V rows, 16 KB each
+    static constexpr int kQ = 2 * kTileBytes;                     // two q rows (bf16)
+    static constexpr int kScore = kQ + 2 * kHeadDim * 2;          // float[2][64]
+    static constexpr int kBar = kScore + 2 * kPageTokens * 4;
+    static constexpr int kStats = kBar + 8;                       // float[2][2]: row maximum and row sum per query head
+    static constexpr int kTotal = kStats + 16;
+};
+
+template <bool kFused>
+__global__ void __launch_bounds__(kShortThreads) qm_decode_short_kernel(const DecodeArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char* ktile = smem + ShortSmem::kTile;
+    unsigned char* vtile = ktile + kTileBytes;
+    unsigned char* qrows = smem + ShortSmem::kQ;
+    float* score = reinterpret_cast<float*>(smem + ShortSmem::kScore);
+    const uint32_t bar = smem_addr(smem + ShortSmem::kBar);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hkv = a.kv_heads;
+    const int stream = blockIdx.x / hkv;
+    const int head = blockIdx.x - stream * hkv;
+    const int seg = blockIdx.x;
+
+    pdl_trigger();
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+    }
+    pdl_wait();
+    const int len = clamp_len(a.seq_lens[stream] + a.len_offset, 1, a.status);       // keys to attend, at most one page
+    int page_id = a.page_table[(size_t)stream * a.max_pages];
+    if (page_id < 0 || page_id >= a.num_pages) {
+        if (tid == 0 && len > 0) atomicOr(a.status, QM_DEVSTAT_BAD_PAGE);
+        page_id = 0;
+    }
+    const size_t row0 = (size_t)seg * 2;                  // the two query rows of this KV head
+    if (len == 0) {                                       // nothing to attend: zero row / empty partial
+        for (int i = tid; i < 2 * kHeadDim; i += kShortThreads) {
+            const size_t row = row0 + i / kHeadDim;
+            const int d = i % kHeadDim;
+            if (a.mode == 0) {
+                a.out[row * kHeadDim + d] = 0;
+            } else {
+                float* dst = a.partial_out + row * kPartialStride;
+                dst[2 + d] = 0.0f;
+                if (d == 0) {
+                    dst[0] = -CUDART_INF_F;
+                    dst[1] = 0.0f;
+                }
+            }
+        }
+        return;
+    }
+    const size_t tile = ((size_t)page_id * hkv + head) * kTileElems;
+    const int stored = kFused ? len - 1 : len;            // rows already in the pool
+    __syncthreads();                                      // the barrier is initialised
+    bool dead = false;
+    if (tid == 0) {
+        const uint32_t bytes = (uint32_t)stored * (kHeadDim * 2);
+        mbar_arrive_expect_tx(bar, 2 * bytes);
+        if (bytes) {
+            bulk_copy_g2s(smem_addr(ktile), a.key_pool + tile, bytes, bar);
+            bulk_copy_g2s(smem_addr(vtile), a.value_pool + tile, bytes, bar);
+        }
+    }
+    if (kFused) {
+        // warps 0, 1: the two q rows; warp 2: the new token's K row; warp 3: its V row
+        int position = len - 1;
+        if (position >= a.rope_rows) {
+            if (tid == 0) atomicOr(a.status, QM_DEVSTAT_BAD_POS);
+            position = a.rope_rows - 1;
+        }
+        const uint2 craw = *reinterpret_cast<const uint2*>(a.rope_cos + (size_t)position * kHeadDim + 4 * lane);
+        const uint2 sraw = *reinterpret_cast<const uint2*>(a.rope_sin + (size_t)position * kHeadDim + 4 * lane);
+        const float c[4] = {bf16_lo(craw.x), bf16_hi(craw.x), bf16_lo(craw.y), bf16_hi(craw.y)};
+        const float sn[4] = {bf16_lo(sraw.x), bf16_hi(sraw.x), bf16_lo(sraw.y), bf16_hi(sraw.y)};
+        const size_t new_row = tile + (size_t)(len - 1) * kHeadDim + 4 * lane;
+        if (warp < 2) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(a.q_rot + (row0 + warp) * kHeadDim + 4 * lane);
+            const uint2 wq = *reinterpret_cast<const uint2*>(a.q_norm_weight + 4 * lane);
+            *reinterpret_cast<uint2*>(qrows + warp * 256 + lane * 8) = norm_rope_row(raw, wq, c, sn, lane, a.epsilon);
+        } else if (warp == 2) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(a.raw_k + (size_t)seg * kHeadDim + 4 * lane);
+            const uint2 wk = *reinterpret_cast<const uint2*>(a.k_norm_weight + 4 * lane);
+            const uint2 krow = norm_rope_row(raw, wk, c, sn, lane, a.epsilon);
+            *reinterpret_cast<uint2*>(ktile + (len - 1) * (kHeadDim * 2) + lane * 8) = krow;
+            *reinterpret_cast<uint2*>(a.key_pool + new_row) = krow;
+        } else {
+            const uint2 vrow = *reinterpret_cast<const uint2*>(a.raw_v + (size_t)seg * kHeadDim + 4 * lane);
+            *reinterpret_cast<uint2*>(vtile + (len - 1) * (kHeadDim * 2) + lane * 8) = vrow;
+            *reinterpret_cast<uint2*>(a.value_pool + new_row) = vrow;
+        }
+    } else if (warp < 2) {
+        *reinterpret_cast<uint2*>(qrows + warp * 256 + lane * 8) =
+            *reinterpret_cast<const uint2*>(a.q_rot + (row0 + warp) * kHeadDim + 4 * lane);
+    }
+    if (!mbar_wait_bounded(bar, 0, dead) && lane == 0) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+    __syncthreads();
+
+    // ---- scores in the log2 domain: half-warp per key row, 8 keys per pass over the four warps
+    const int half = lane >> 4, lp = lane & 15;
+    const float qscale = kLog2e / sqrtf((float)kHeadDim);
+    float2 q0[4], q1[4];
+    {
+        const uint4 qa = *reinterpret_cast<const uint4*>(qrows + lp * 16);
+        const uint4 qb = *reinterpret_cast<const uint4*>(qrows + 256 + lp * 16);
+        const float2 qs2 = make_float2(qscale, qscale);
+        q0[0] = fmul2(bf16x2_to_float2(qa.x), qs2); q0[1] = fmul2(bf16x2_to_float2(qa.y), qs2);
+        q0[2] = fmul2(bf16x2_to_float2(qa.z), qs2); q0[3] = fmul2(bf16x2_to_float2(qa.w), qs2);
+        q1[0] = fmul2(bf16x2_to_float2(qb.x), qs2); q1[1] = fmul2(bf16x2_to_float2(qb.y), qs2);
+        q1[2] = fmul2(bf16x2_to_float2(qb.z), qs2); q1[3] = fmul2(bf16x2_to_float2(qb.w), qs2);
+    }
+    for (int key0 = 0; key0 < len; key0 += 8) {
+        const int key = key0 + 2 * warp + half;
+        float d0 = 0.0f, d1 = 0.0f;
+        if (key < len) {
+            const uint4 kk = *reinterpret_cast<const uint4*>(ktile + key * (kHeadDim * 2) + lp * 16);
+            const float2 kf[4] = {bf16x2_to_float2(kk.x), bf16x2_to_float2(kk.y), bf16x2_to_float2(kk.z), bf16x2_to_float2(kk.w)};
+            float2 s0 = make_float2(0.0f, 0.0f), s1 = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                s0 = ffma2(q0[j], kf[j], s0);
+                s1 = ffma2(q1[j], kf[j], s1);
+            }
+            d0 = s0.x + s0.y;
+            d1 = s1.x + s1.y;
+        }
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) {
+            d0 += __shfl_xor_sync(0xffffffffu, d0, off);
+            d1 += __shfl_xor_sync(0xffffffffu, d1, off);
+        }
+        if (lp == 0 && key < len) {
+            score[key] = d0;
+            score[kPageTokens + key] = d1;
+        }
+    }
+    __syncthreads();
+
+    // ---- softmax: warp qh owns query head qh; probabilities replace the scores
+    float* stats = reinterpret_cast<float*>(smem + ShortSmem::kStats);
+    if (warp < 2) {
+        float* sc = score + warp * kPageTokens;
+        const float x0 = lane < len ? sc[lane] : -CUDART_INF_F;
+        const float x1 = lane + 32 < len ? sc[lane + 32] : -CUDART_INF_F;
+        float m = fmaxf(x0, x1);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        const float p0 = lane < len ? fast_exp2(x0 - m) : 0.0f;
+        const float p1 = lane + 32 < len ? fast_exp2(x1 - m) : 0.0f;
+        float l = p0 + p1;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+        sc[lane] = p0;
+        sc[lane + 32] = p1;
+        if (lane == 0) {
+            stats[2 * warp] = m;
+            stats[2 * warp + 1] = l;
+        }
+    }
+    __syncthreads();
+
+    // ---- O = P V: thread = (query head, two output dimensions)
+    {
+        const int qh = tid >> 6, dp = tid & 63;
+        const float* pr = score + qh * kPageTokens;
+        float2 acc = make_float2(0.0f, 0.0f);
+        for (int key = 0; key < len; ++key) {
+            const float p = pr[key];
+            const float2 vv = bf16x2_to_float2(*reinterpret_cast<const uint32_t*>(vtile + key * (kHeadDim * 2) + dp * 4));
+            acc = ffma2(make_float2(p, p), vv, acc);
+        }
+        const float m = stats[2 * qh];
+        const float l = stats[2 * qh + 1];
+        const size_t row = row0 + qh;
+        if (a.mode == 0) {
+            *reinterpret_cast<uint32_t*>(a.out + row * kHeadDim + 2 * dp) =
+                f32_to_bf16_bits(acc.x / l) | (f32_to_bf16_bits(acc.y / l) << 16);
+        } else {
+            float* dst = a.partial_out + row * kPartialStride;
+            *reinterpret_cast<float2*>(dst + 2 + 2 * dp) = acc;
+            if (dp == 0) {
+                dst[0] = m * kLn2;
+                dst[1] = l;
+            }
+        }
+    }
+}
+
 // partials [parts][rows][130] (m in natural-log domain) -> out [rows][128] bf16.
 __global__ void __launch_bounds__(128) qm_combine_partials_kernel(const float* __restrict__ partials, int parts,
                                                                   int rows, uint16_t* __restrict__ out) {
@@ -771,6 +969,20 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
         if (fused) {
             a.raw_k = fused->k + (size_t)begin * pool->kv_heads * kHeadDim;
             a.raw_v = fused->v + (size_t)begin * pool->kv_heads * kHeadDim;
+        }
+        if (max_pages == 1) {
+            // every stream fits one page: one small CTA per (stream, kv head), no scratch involved
+            const dim3 short_grid((unsigned)(n * pool->kv_heads));
+            if (fused) {
+                QM_CUDA_TRY(qm_launch(qm_decode_short_kernel<true>, short_grid, dim3(kShortThreads), ShortSmem::kTotal, stream, a),
+                            "fused decode step launch (short contexts)");
+            } else {
+                QM_CUDA_TRY(qm_launch(qm_decode_short_kernel<false>, short_grid, dim3(kShortThreads), ShortSmem::kTotal, stream, a),
+                            "decode attention launch (short contexts)");
+            }
+            continue;
+        }
+        if (fused) {
             QM_CUDA_TRY(qm_launch(qm_decode_splitkv_kernel<true>, dim3(grid), dim3(kDecodeThreads), SharedLayout::kTotal,
                                   stream, a),
                         "fused decode step launch");

@@ -214,3 +214,10 @@ def test_lengths_written_by_the_launch_just_before(qm):
         assert eng.status() == 0
     finally:
         eng.close()
+
+
+def test_short_contexts_one_page_per_stream(qm):
+    """Every stream within one page: the dedicated short-context kernel (one CTA per stream and KV head) serves the
+    call - same checks as any other step, including the partial + combine path and an empty stream."""
+    check_step(qm, scenario.DecodeScenario(seed=31, lengths=[0, 1, 5, 16, 17, 33, 62, 63, 40, 2, 31, 32]))
+    check_step(qm, scenario.DecodeScenario(seed=32, lengths=[63] * 70, random_weights=True))

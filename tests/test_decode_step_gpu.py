@@ -35,6 +35,8 @@ def run_fused(qm, sc):
 
 @pytest.mark.parametrize("lengths,heads", [([512], (16, 8)), ([0, 1, 63, 64, 65, 127, 128], (16, 8)),
                                            ([9000, 3, 4100, 700], (16, 8)), ([5] * 200 + [130] * 9, (16, 8)),
+                                           ([0, 1, 15, 16, 31, 40, 62, 63, 7, 33], (16, 8)),    # one page per stream: short-context kernel
+                                           ([2, 63], (4, 2)),
                                            ([100, 257], (4, 2))])
 def test_fused_step_equals_append_then_attention(qm, lengths, heads):
     sc = scenario.DecodeScenario(seed=70 + len(lengths), lengths=lengths, q_heads=heads[0], kv_heads=heads[1],
