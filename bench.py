@@ -55,8 +55,11 @@ def splitmix64_ints(seed, lo, hi, n):
 
 
 def workload_lengths(rank=0):
-    """Existing KV length per stream; the timed step appends one token and attends length + 1 keys."""
-    return splitmix64_ints(1 * 1000 + 99 + 7919 * rank, LEN_LO, LEN_HI, BATCH)
+    """Existing KV length per stream; the timed step appends one token and attends length + 1 keys.  Every rank
+    serves its own 64 streams with the same length draw (its cache contents, page ids and activations differ), so
+    that the work per GPU is the same at every N - what weak scaling means."""
+    del rank
+    return splitmix64_ints(1 * 1000 + 99, LEN_LO, LEN_HI, BATCH)
 
 
 def algorithmic_bytes_per_layer(lengths):
