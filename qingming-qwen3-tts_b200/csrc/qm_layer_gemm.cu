@@ -35,6 +35,8 @@ struct GemmArgs {
     uint16_t* out[3];            // [M][N]  (SwiGLU: N = intermediate)
     int out_cols[3];             // N of each segment
     int first_tile[3];           // tile index where each segment starts
+    const uint16_t* weight[3];   // raw weight pointers [N][K] (SwiGLU: gate, up), for the L2 warm-up
+    int k_dim;                   // K
     const uint16_t* residual;    // [M][N] or null (single-segment calls)
     uint32_t* status;
     int rows;                    // M
@@ -186,6 +188,25 @@ qm_skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_co
         }
         __syncwarp();
     } else {
+        // ------------------------------------------------- L2 warm-up of this CTA's weight slice
+        // Still before the dependency wait: weights are constants.  The ring above holds only its first stages;
+        // here every thread asks the L2 for one weight row's share of this CTA's K range, so that HBM streams the
+        // whole slice while the previous kernel finishes and the ring's later loads find their bytes in L2.
+        {
+            const uint16_t* wbase;
+            int wrow;
+            if (kEpilogue == EPI_SWIGLU) {
+                wbase = tid < 64 ? a.weight[0] : a.weight[1];
+                wrow = tile * 64 + (tid & 63);
+            } else {
+                wbase = a.weight[seg];
+                wrow = tile * kTileRows + tid;
+            }
+            // (the ring's own first stages are already on their way)
+            if (wrow < a.out_cols[seg] && n_chunks > head)
+                bulk_prefetch_l2_hint(wbase + (size_t)wrow * a.k_dim + (size_t)(chunk_begin + head) * kChunkCols,
+                                      (uint32_t)((n_chunks - head) * kChunkCols * 2), l2_policy_evict_last());
+        }
         // ------------------------------------------------- partial sums -> own shared memory
         if (!mbar_wait_bounded(acc_bar, 0, dead) && lane == 0) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
         tc_fence_after();
@@ -379,6 +400,7 @@ int32_t run_gemm(const uint16_t* x, const Segment* segs, int n_segs, const uint1
         int32_t rc = encode_matrix_map(&maps[i], wptr, (uint64_t)sg.out_cols, (uint64_t)k_dim, (uint32_t)rows_per_tile);
         if (rc != QM_OK) return rc;
         a.first_tile[i] = i < n_segs ? tiles : 0x7fffffff;
+        a.weight[i] = wptr;
         if (i < n_segs) {
             a.bias[i] = sg.bias;
             a.out[i] = sg.out;
@@ -389,6 +411,7 @@ int32_t run_gemm(const uint16_t* x, const Segment* segs, int n_segs, const uint1
     int32_t rc = encode_matrix_map(&x_map, x, (uint64_t)rows, (uint64_t)k_dim, (uint32_t)m_pad);
     if (rc != QM_OK) return rc;
     a.residual = residual;
+    a.k_dim = k_dim;
     a.status = status;
     a.rows = rows;
     a.chunks = k_dim / kChunkCols;
