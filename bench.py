@@ -153,11 +153,27 @@ def host_cores():
         return os.cpu_count() or 1
 
 
+def use_all_host_threads():
+    """The CPU legs run OpenMP loops; a launcher (torchrun) may have exported OMP_NUM_THREADS=1 for its workers.
+    Returns the thread count in use."""
+    import ctypes
+
+    cores = host_cores()
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(cores)
+    except OSError:
+        cores = int(os.environ.get("OMP_NUM_THREADS", cores))
+    return cores
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from oracle import qm_oracle as oracle
+
+    oracle.lib()
+    use_all_host_threads()
 
     lengths = workload_lengths()
     sample = list(range(BATCH))                  # one layer of the whole 64-stream batch per step
@@ -849,6 +865,8 @@ def cpu_baseline_and_parity(eng, q_rot0, out0, lengths, table):
 
     from oracle import qm_oracle as oracle
 
+    oracle.lib()
+    use_all_host_threads()
     sample = list(range(BATCH))
     kview, vview = eng.pool_view(0)
     kpool = kview.view(torch.int16).cpu().numpy().view(np.uint16)
