@@ -17,6 +17,7 @@ void qmo_append(const uint16_t*, const uint16_t*, const uint16_t*, const uint16_
 int qmo_decode_attention_batch(const uint16_t*, const uint16_t* const*, const uint16_t* const*, const int32_t*,
                                const int32_t*, int, int, int, int, uint16_t*, float*);
 float qmo_bf16_to_f32(uint16_t);
+int qmo_final_head_sample(const uint16_t*, int, int32_t*, int, int, int, int, int, int, float, uint64_t*, float*);
 }
 
 template <class T>
@@ -85,6 +86,32 @@ int main() {
             threw = std::string(e.what()).find("attention launch") != std::string::npos;
         }
         if (!threw) { std::printf("invalid layer did not throw\n"); return 4; }
+
+        // the end of a step: logits -> code (greedy, with the reference's processors) -> embedding row
+        const int vocab = 3072, hidden = 256;
+        std::vector<uint16_t> logits(vocab), table_rows((size_t)vocab * hidden);
+        qmo_fill_normal_bf16(21, logits.data(), vocab);
+        qmo_fill_normal_bf16(22, table_rows.data(), (int64_t)table_rows.size());
+        std::vector<int32_t> history(8192, 0), generation = {3};
+        history[0] = 5; history[1] = 6; history[2] = 7;
+        uint64_t state = 99;
+        std::vector<int32_t> history_copy = history;
+        const int want_code = qmo_final_head_sample(logits.data(), vocab, history_copy.data(), 8192, 3, 7, 2150, vocab - 1024, 0,
+                                                    0.9f, &state, nullptr);
+        qm::DeviceBuffer dlogits, dtable, dhist, dgen, dcode(sizeof(int32_t)), drow(hidden * 2);
+        upload(logits, dlogits); upload(table_rows, dtable); upload(history, dhist); upload(generation, dgen);
+        engine.final_head_sample(dlogits.as<uint16_t>(), 1, vocab, dhist.as<int32_t>(), 8192, dgen.as<int32_t>(),
+                                 QM_SAMPLE_REPETITION | QM_SAMPLE_SUPPRESS | QM_SAMPLE_RECORD, 0, 0.9f, nullptr, dcode.as<int32_t>());
+        engine.gather_embeddings(dtable.as<uint16_t>(), dcode.as<int32_t>(), 1, vocab, hidden, drow.as<uint16_t>());
+        cudaStreamSynchronize(stream);
+        int32_t code = -1, recorded = -1;
+        std::vector<uint16_t> row(hidden);
+        cudaMemcpy(&code, dcode.pointer, sizeof(code), cudaMemcpyDeviceToHost);
+        cudaMemcpy(&recorded, dhist.as<int32_t>() + 3, sizeof(recorded), cudaMemcpyDeviceToHost);
+        cudaMemcpy(row.data(), drow.pointer, hidden * 2, cudaMemcpyDeviceToHost);
+        if (code != want_code || recorded != want_code) { std::printf("final head: code %d, oracle %d, recorded %d\n", code, want_code, recorded); return 5; }
+        for (int i = 0; i < hidden; ++i)
+            if (row[i] != table_rows[(size_t)code * hidden + i]) { std::printf("embedding row differs at %d\n", i); return 6; }
     } catch (const std::exception& e) {
         std::printf("exception: %s\n", e.what());
         return 1;

@@ -120,3 +120,29 @@ def test_argument_checks(engine, qm):
         engine.final_head_sample(logits, top_k=50)            # sampling without a state
     with pytest.raises(qm.QmError):
         engine.final_head_sample(logits, flags=sc.REPETITION)  # penalty without a history
+
+
+def test_degenerate_rows(engine):
+    """Rows where nothing is finite, where everything is equal, a vocabulary smaller than the sort size, and a top_k
+    beyond the vocabulary: same answers as the restated reference chain, and no draw is consumed when the weights do
+    not add up to something positive (the reference returns before drawing)."""
+    import torch
+
+    vocab = 2048
+    rows = {
+        "all_minus_inf": np.full(vocab, -np.inf, dtype=np.float32),
+        "all_equal": np.full(vocab, 1.25, dtype=np.float32),
+        "one_finite": np.where(np.arange(vocab) == 777, 3.0, -np.inf).astype(np.float32),
+        "ramp": np.linspace(-4, 4, vocab, dtype=np.float32),
+    }
+    for top_k in (0, 50, 5000):
+        for name, values in rows.items():
+            bits = oracle.f32_to_bf16(values)
+            logits = torch.from_numpy(bits.view(np.int16)[None]).cuda().view(torch.bfloat16)
+            state = torch.tensor([12345], dtype=torch.int64, device="cuda")
+            code = engine.final_head_sample(logits, flags=0, top_k=top_k, temperature=0.9, rng_state=state)
+            torch.cuda.synchronize()
+            want = oracle.final_head_sample(bits, flags=0, top_k=top_k, temperature=0.9, rng_state=12345)
+            assert int(code.cpu()[0]) == want[0], (name, top_k)
+            assert int(state.cpu().numpy().astype(np.uint64)[0]) == want[2], (name, top_k)
+    assert engine.status() == 0
