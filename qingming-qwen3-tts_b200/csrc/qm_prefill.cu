@@ -228,23 +228,29 @@ qm_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             issue_s(1, 0);
             tc_commit(bar(BAR_SFULL + 1));
             tc_commit(bar(BAR_KEMPTY + 0));
+            // Barriers that are normally complete by the time they are needed (V, the next K, P of the second
+            // head) are probed before the preceding batch of MMAs, so their round trip overlaps the issue.
+            uint32_t v_seen = mbar_probe(bar(BAR_VFULL + 0), 0);
             for (int j = 0; j < n_tiles; ++j) {
                 const int vst = j % kKvStages;
                 const int kst = (j + 1) % kKvStages;
                 const bool more = j + 1 < n_tiles;
-                if (!mbar_wait_bounded(bar(BAR_VFULL + vst), (j / kKvStages) & 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                if (!mbar_wait_probed(v_seen, bar(BAR_VFULL + vst), (j / kKvStages) & 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
                 if (!mbar_wait_bounded(bar(BAR_PREADY + 0), j & 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                const uint32_t k_seen = more ? mbar_probe(bar(BAR_KFULL + kst), ((j + 1) / kKvStages) & 1) : 1u;
+                const uint32_t p1_seen = mbar_probe(bar(BAR_PREADY + 1), j & 1);
                 tc_fence_after();
                 issue_pv(0, vst, j > 0);
                 tc_commit(bar(BAR_OREADY + 0));
                 if (more) {
-                    if (!mbar_wait_bounded(bar(BAR_KFULL + kst), ((j + 1) / kKvStages) & 1, dead))
+                    if (!mbar_wait_probed(k_seen, bar(BAR_KFULL + kst), ((j + 1) / kKvStages) & 1, dead))
                         atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
                     tc_fence_after();
                     issue_s(0, kst);
                     tc_commit(bar(BAR_SFULL + 0));
                 }
-                if (!mbar_wait_bounded(bar(BAR_PREADY + 1), j & 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                if (!mbar_wait_probed(p1_seen, bar(BAR_PREADY + 1), j & 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                v_seen = more ? mbar_probe(bar(BAR_VFULL + kst), ((j + 1) / kKvStages) & 1) : 1u;
                 tc_fence_after();
                 issue_pv(1, vst, j > 0);
                 tc_commit(bar(BAR_OREADY + 1));
