@@ -491,8 +491,53 @@ def run_prefill_section(pkg, steps, warmup, n_seqs=8):
         torch.cuda.synchronize()
         append_ms.append(e[0].elapsed_time(e[1]))
         attn_ms.append(e[1].elapsed_time(e[2]))
+    # ---- one whole decoder layer of the prefill loop over the same tokens (17.cu:16700-16880): input norm, q/k/v
+    # projections, norm + RoPE + scatter, attention, o-projection + residual, post-norm, gate/up + SwiGLU,
+    # down-projection + residual; weights ~ N(0, 0.02) in the 1.7B talker shape
+    hidden_dim, inter = 2048, 6144
+    nq, nk = Q_HEADS * D, KV_HEADS * D
+
+    def weight(*shape):
+        return (torch.randn(*shape, generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+
+    w_q, w_k, w_v, w_o = weight(nq, hidden_dim), weight(nk, hidden_dim), weight(nk, hidden_dim), weight(hidden_dim, nq)
+    w_gate, w_up, w_down = weight(inter, hidden_dim), weight(inter, hidden_dim), weight(hidden_dim, inter)
+    norm_w = torch.ones(hidden_dim, dtype=torch.bfloat16, device="cuda")
+    hidden_rows = torch.randn(total, hidden_dim, generator=gen, device="cuda").to(torch.bfloat16)
+
+    def buf(cols):
+        return torch.empty((total, cols), dtype=torch.bfloat16, device="cuda")
+
+    normed, residual, post, act, nxt = buf(hidden_dim), buf(hidden_dim), buf(hidden_dim), buf(inter), buf(hidden_dim)
+    ql, kl, vl = buf(nq), buf(nk), buf(nk)
+
+    def layer():
+        eng.launch_rmsnorm(hidden_rows, norm_w, out=normed)
+        eng.linear_generic(normed, w_q, out=ql)
+        eng.linear_generic(normed, w_k, out=kl)
+        eng.linear_generic(normed, w_v, out=vl)
+        eng.prefill_norm_rope_scatter(0, ql.view(total, Q_HEADS, D), kl.view(total, KV_HEADS, D), vl.view(total, KV_HEADS, D),
+                                      ones, ones, cu_dev, page_table, q_rot=q_rot)
+        eng.launch_attention_prefill(0, q_rot, cu_dev, page_table, max_len, out=out)
+        eng.linear_generic(out.view(total, nq), w_o, residual=hidden_rows, out=residual)
+        eng.launch_rmsnorm(residual, norm_w, out=post)
+        eng.gate_up_swiglu_rows(post, w_gate, w_up, out=act)
+        eng.linear_generic(act, w_down, residual=residual, out=nxt)
+
+    for _ in range(3):
+        layer()
+    torch.cuda.synchronize()
+    layer_ms = []
+    for _ in range(steps):
+        e[0].record()
+        layer()
+        e[1].record()
+        torch.cuda.synchronize()
+        layer_ms.append(e[0].elapsed_time(e[1]))
     status = eng.status()
     flops = float(sum(4096 * int(n) * (int(n) + 1) for n in lengths))
+    projection_flops = 2.0 * total * (hidden_dim * (nq + 2 * nk) + nq * hidden_dim + 3 * hidden_dim * inter)
+    layer_mean = float(np.mean(layer_ms))
     attn = float(np.mean(attn_ms))
     peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
     burst = float(peaks.get("bf16_tflops", 1590.0))
@@ -505,6 +550,10 @@ def run_prefill_section(pkg, steps, warmup, n_seqs=8):
         "frac_of_measured_burst_peak": tflops / burst, "frac_of_measured_sustained_peak": tflops / sustained,
         "peak_tflops_burst": burst, "peak_tflops_sustained": sustained, "device_status": status,
         "append_gbs": total * (Q_HEADS + 2 * KV_HEADS) * D * 2 * 2 / (float(np.mean(append_ms)) * 1e-3) / 1e9,
+        "layer": {"what": "one whole prefill decoder layer on the same tokens, 10 launches of this library",
+                  "ms": layer_mean, "projection_flops": projection_flops,
+                  "tflops": (flops + projection_flops) / (layer_mean * 1e-3) / 1e12,
+                  "prompt_tokens_per_s_28_layers": total / (28 * layer_mean * 1e-3)},
     }
     eng.close()
     return result

@@ -297,6 +297,20 @@ int32_t qm_qkv_linear(qm_kv_pool* pool, const uint16_t* x, const uint16_t* q_wei
 int32_t qm_gate_up_swiglu(qm_kv_pool* pool, const uint16_t* x, const uint16_t* gate_weight, const uint16_t* up_weight,
                           uint16_t* out, int32_t rows, int32_t hidden, int32_t intermediate, void* stream);
 
+/* ---- the same projections for many token rows at once (prefill) ----
+ * linear_bf16 as the prefill loop calls it through linear_generic (17.cu:142-289; call sites :16730-16860), any
+ * number of rows: out[r][n] = bf16(dot(x[r], weight[n]) + bias[n]); with `residual` (the loop's launch_add),
+ * bf16(residual[r][n] + that value).  out_features and in_features multiples of 64; bias and residual may be NULL.
+ * Persistent tcgen05 kernel, 128 x 256 tiles, fp32 accumulation in TMEM. */
+int32_t qm_linear_rows(qm_kv_pool* pool, const uint16_t* x, const uint16_t* weight, const uint16_t* bias,
+                       const uint16_t* residual, uint16_t* out, int32_t rows, int32_t out_features, int32_t in_features,
+                       void* stream);
+
+/* The prefill loop's two linear_generic calls on post_norm_ (gate, up) and its swiglu_kernel (17.cu:8771-8800,
+ * call sites :16833-16860) in one launch: out[r][c] = bf16( bf16(silu(bf16(gate))) * bf16(up) ). */
+int32_t qm_gate_up_swiglu_rows(qm_kv_pool* pool, const uint16_t* x, const uint16_t* gate_weight, const uint16_t* up_weight,
+                               uint16_t* out, int32_t rows, int32_t hidden, int32_t intermediate, void* stream);
+
 /* ---- the end of a decode step: codec-head logits -> next code, and the embedding rows of the next step ---- */
 
 #define QM_SAMPLE_REPETITION 1   /* repetition penalty 1.05 over the stream's history (17.cu:14063-14099)     */

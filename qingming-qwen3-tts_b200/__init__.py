@@ -81,6 +81,8 @@ ABI = {
     "qm_linear": (c_int32, [c_void_p] * 6 + [c_int32, c_int32, c_int32, c_void_p]),
     "qm_qkv_linear": (c_int32, [c_void_p] * 11 + [c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "qm_gate_up_swiglu": (c_int32, [c_void_p] * 5 + [c_int32, c_int32, c_int32, c_void_p]),
+    "qm_linear_rows": (c_int32, [c_void_p] * 6 + [c_int32, c_int32, c_int32, c_void_p]),
+    "qm_gate_up_swiglu_rows": (c_int32, [c_void_p] * 5 + [c_int32, c_int32, c_int32, c_void_p]),
     "qm_final_head_sample": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_int32, c_void_p, c_int32, c_int32,
                                        c_int32, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
     "qm_embedding_gather": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
@@ -319,6 +321,27 @@ class TalkerAttention:
             out = torch.empty((x.shape[0], gate_weight.shape[0]), dtype=torch.bfloat16, device="cuda")
         _check(self.lib.qm_gate_up_swiglu(self.pool, _ptr(x), _ptr(gate_weight), _ptr(up_weight), _ptr(out), x.shape[0],
                                           x.shape[1], gate_weight.shape[0], _stream()))
+        return out
+
+    def linear_generic(self, x, weight, bias=None, residual=None, out=None):
+        """linear_generic of the reference's prefill loop (17.cu:16730-16860) for any number of token rows; with
+        `residual`, the loop's launch_add is folded in."""
+        import torch
+
+        if out is None:
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16, device="cuda")
+        _check(self.lib.qm_linear_rows(self.pool, _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), x.shape[0],
+                                       weight.shape[0], weight.shape[1], _stream()))
+        return out
+
+    def gate_up_swiglu_rows(self, x, gate_weight, up_weight, out=None):
+        """Gate and up projections plus swiglu_kernel (17.cu:8771) of the prefill loop, any number of rows."""
+        import torch
+
+        if out is None:
+            out = torch.empty((x.shape[0], gate_weight.shape[0]), dtype=torch.bfloat16, device="cuda")
+        _check(self.lib.qm_gate_up_swiglu_rows(self.pool, _ptr(x), _ptr(gate_weight), _ptr(up_weight), _ptr(out),
+                                               x.shape[0], x.shape[1], gate_weight.shape[0], _stream()))
         return out
 
     def final_head_sample(self, logits, generation_index=None, history=None, flags=0, eos_token=2150,

@@ -433,6 +433,254 @@ int32_t run_gemm(const uint16_t* x, const Segment* segs, int n_segs, const uint1
     return QM_OK;
 }
 
+
+// ---- many token rows (prefill): persistent 128 x 256 output tiles ------------------------------------------------
+//
+// Stands in for linear_bf16 / linear_warp32_bf16x2_f32acc_kernel (17.cu:142-289) as the prefill loop calls it
+// through linear_generic (17.cu:16730-16860), with the residual add (launch_add) and the elementwise SwiGLU
+// (swiglu_kernel, 17.cu:8771) of that loop folded into the epilogue at the same bf16 materialisation points.
+//
+// One CTA per SM walks output tiles of 128 token rows x 256 weight rows; per 64-column K chunk the TMA warp brings a
+// 16 KB activation tile and a 32 KB weight tile (two 128-row boxes: consecutive weight rows, or 128 gate rows and
+// the matching 128 up rows), the MMA thread issues four 128 x 256 x 16 tcgen05.mma into one of two 256-column
+// TMEM accumulators, and the four epilogue warps drain the other accumulator meanwhile.
+constexpr int kRowsBM = 128;
+constexpr int kRowsBN = 256;
+constexpr int kRowsStages = 4;
+constexpr int kRowsThreads = 192;
+constexpr int kRowsStageA = kRowsBM * kChunkCols * 2;      // 16 KB
+constexpr int kRowsStageB = kRowsBN * kChunkCols * 2;      // 32 KB
+constexpr int kRowsStageBytes = kRowsStageA + kRowsStageB;
+
+struct RowsSmem {
+    static constexpr int kRing = 0;
+    static constexpr int kBars = kRowsStages * kRowsStageBytes;            // full[4], empty[4], acc_full[2], acc_empty[2]
+    static constexpr int kTmemSlot = kBars + (2 * kRowsStages + 4) * 8;
+    static constexpr int kTotal = kTmemSlot + 16;
+};
+
+struct RowsArgs {
+    const uint16_t* bias;        // [n_cols] or null
+    const uint16_t* residual;    // [rows][n_cols] or null
+    uint16_t* out;               // [rows][n_cols]
+    uint32_t* status;
+    int rows;
+    int n_cols;                  // output columns
+    int k_chunks;
+    int m_tiles;
+    int n_tiles;
+};
+
+template <bool kSwiglu>
+__global__ void __launch_bounds__(kRowsThreads, 1)
+qm_rows_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w0_map,
+                    const __grid_constant__ CUtensorMap w1_map, const RowsArgs a) {
+    constexpr int kColsPerTile = kSwiglu ? 128 : 256;
+    pdl_trigger();
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw_addr = smem_addr(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    unsigned char* smem = smem_raw + pad;
+    const uint32_t sbase = raw_addr + pad;
+    const uint32_t bar0 = sbase + RowsSmem::kBars;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kRowsStages + s); };
+    auto acc_full = [&](int b) { return bar0 + 8u * (2 * kRowsStages + b); };
+    auto acc_empty = [&](int b) { return bar0 + 8u * (2 * kRowsStages + 2 + b); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + RowsSmem::kTmemSlot);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kRowsStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), 128);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_addr(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    const int total_tiles = a.m_tiles * a.n_tiles;
+    bool dead = false;
+    pdl_wait();
+
+    if (warp == 5) {
+        if (lane == 0) {
+            int it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                const int m0 = (tile / a.n_tiles) * kRowsBM;
+                const int n0 = (tile % a.n_tiles) * kColsPerTile;
+                for (int kc = 0; kc < a.k_chunks; ++kc, ++it) {
+                    const int st = it % kRowsStages;
+                    if (!mbar_wait_bounded(empty_bar(st), ((it / kRowsStages) & 1) ^ 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                    const uint32_t dst = sbase + RowsSmem::kRing + st * kRowsStageBytes;
+                    mbar_arrive_expect_tx(full_bar(st), kRowsStageBytes);
+                    tma_load_2d(dst, &x_map, full_bar(st), kc * kChunkCols, m0);
+                    tma_load_2d(dst + kRowsStageA, &w0_map, full_bar(st), kc * kChunkCols, n0);
+                    if (kSwiglu)
+                        tma_load_2d(dst + kRowsStageA + kRowsStageB / 2, &w1_map, full_bar(st), kc * kChunkCols, n0);
+                    else
+                        tma_load_2d(dst + kRowsStageA + kRowsStageB / 2, &w0_map, full_bar(st), kc * kChunkCols, n0 + 128);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 4) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_instr_desc(kRowsBM, kRowsBN, false);
+            int it = 0, local = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                if (!mbar_wait_bounded(acc_empty(buf), ((local >> 1) & 1) ^ 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                tc_fence_after();
+                for (int kc = 0; kc < a.k_chunks; ++kc, ++it) {
+                    const int st = it % kRowsStages;
+                    if (!mbar_wait_bounded(full_bar(st), (it / kRowsStages) & 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                    tc_fence_after();
+                    const uint32_t xa = sbase + RowsSmem::kRing + st * kRowsStageBytes;
+                    const uint32_t wa = xa + kRowsStageA;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks)
+                        mma_ss(tmem_base + buf * 256, smem_desc(xa + ks * 32, 16, 1024), smem_desc(wa + ks * 32, 16, 1024), idesc,
+                               (kc > 0 || ks > 0) ? 1u : 0u);
+                    tc_commit(empty_bar(st));
+                }
+                tc_commit(acc_full(buf));
+            }
+        }
+        __syncwarp();
+    } else {
+        const int row_in_tile = warp * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int m0 = (tile / a.n_tiles) * kRowsBM;
+            const int n0 = (tile % a.n_tiles) * kColsPerTile;
+            const int row = m0 + row_in_tile;
+            if (!mbar_wait_bounded(acc_full(buf), (local >> 1) & 1, dead) && lane == 0) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + lane_base + buf * 256;
+#pragma unroll 1
+            for (int c = 0; c < kColsPerTile / 32; ++c) {
+                uint32_t acc[32], acc2[32];
+                tmem_ld32(taddr + c * 32, acc);
+                if (kSwiglu) tmem_ld32(taddr + 128 + c * 32, acc2);
+                tmem_wait_ld();
+                const int col = n0 + c * 32;
+                if (row < a.rows && col < a.n_cols) {
+                    const size_t o = (size_t)row * a.n_cols + col;
+                    uint32_t packed[16];
+                    if (kSwiglu) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            uint32_t bits[2];
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                // bf16(gate), bf16(up), bf16(silu(gate)), bf16(product): 17.cu:8771-8800
+                                const float gv = round_bf16(__uint_as_float(acc[i + h])), u = round_bf16(__uint_as_float(acc2[i + h]));
+                                const float act = round_bf16(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))));
+                                bits[h] = f32_to_bf16_bits(__fmul_rn(act, u));
+                            }
+                            packed[i >> 1] = bits[0] | (bits[1] << 16);
+                        }
+                    } else {
+                        uint4 bias4[4] = {}, res4[4] = {};
+                        if (a.bias)
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) bias4[q] = __ldg(reinterpret_cast<const uint4*>(a.bias + col) + q);
+                        if (a.residual)
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) res4[q] = *(reinterpret_cast<const uint4*>(a.residual + o) + q);
+                        const uint32_t* bias_w = reinterpret_cast<const uint32_t*>(bias4);
+                        const uint32_t* res_w = reinterpret_cast<const uint32_t*>(res4);
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            uint32_t bits[2];
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                // bf16(dot + bias), then bf16(residual + that): 17.cu:234-289 and launch_add
+                                float v = __uint_as_float(acc[i + h]);
+                                const uint32_t bw = (bias_w[i >> 1] >> (16 * h)) & 0xffffu;
+                                if (a.bias) v = __fadd_rn(v, bf16_bits_to_f32((uint16_t)bw));
+                                bits[h] = f32_to_bf16_bits(v);
+                                if (a.residual) {
+                                    const uint32_t rw = (res_w[i >> 1] >> (16 * h)) & 0xffffu;
+                                    bits[h] = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32((uint16_t)rw), bf16_bits_to_f32((uint16_t)bits[h])));
+                                }
+                            }
+                            packed[i >> 1] = bits[0] | (bits[1] << 16);
+                        }
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(a.out + o);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(acc_empty(buf));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+template <bool kSwiglu>
+int32_t run_rows_gemm(const uint16_t* x, const uint16_t* w0, const uint16_t* w1, const uint16_t* bias, const uint16_t* residual,
+                      uint16_t* out, int rows, int n_cols, int k_dim, uint32_t* status, cudaStream_t stream, const char* what) {
+    if (rows < 0 || n_cols < 64 || n_cols % 64 != 0) return qm_fail(QM_EINVAL, "output width must be a positive multiple of 64");
+    if (k_dim < kChunkCols || k_dim % kChunkCols != 0)
+        return qm_fail(QM_EINVAL, "reduction width must be a positive multiple of 64");
+    if (rows == 0) return QM_OK;                      // nothing to do; the row tensors may then be null
+    if (!x || !w0 || !out || (kSwiglu && !w1)) return qm_fail(QM_EINVAL, "null tensor pointer");
+    const uintptr_t all = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w0) | reinterpret_cast<uintptr_t>(w1) |
+                          reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(out);
+    if (all & 15u) return qm_fail(QM_EINVAL, "projection operands must be 16-byte aligned");
+    CUtensorMap x_map, w0_map, w1_map;
+    int32_t rc = encode_matrix_map(&x_map, x, (uint64_t)rows, (uint64_t)k_dim, 128);
+    if (rc != QM_OK) return rc;
+    rc = encode_matrix_map(&w0_map, w0, (uint64_t)n_cols, (uint64_t)k_dim, 128);
+    if (rc != QM_OK) return rc;
+    rc = encode_matrix_map(&w1_map, kSwiglu ? w1 : w0, (uint64_t)n_cols, (uint64_t)k_dim, 128);
+    if (rc != QM_OK) return rc;
+    RowsArgs a{};
+    a.bias = bias;
+    a.residual = residual;
+    a.out = out;
+    a.status = status;
+    a.rows = rows;
+    a.n_cols = n_cols;
+    a.k_chunks = k_dim / kChunkCols;
+    a.m_tiles = (rows + kRowsBM - 1) / kRowsBM;
+    const int cols_per_tile = kSwiglu ? 128 : 256;
+    a.n_tiles = (n_cols + cols_per_tile - 1) / cols_per_tile;
+    const long long tiles = (long long)a.m_tiles * a.n_tiles;
+    if (tiles > 0x7fffffffLL) return qm_fail(QM_ECAPACITY, "too many output tiles for one launch");
+    const int sms = sm_count_of_current_device();
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    auto kernel = qm_rows_gemm_kernel<kSwiglu>;
+    const size_t smem = RowsSmem::kTotal + 1024;
+    QM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), what);
+    QM_CUDA_TRY(qm_launch(kernel, dim3(grid), dim3(kRowsThreads), smem, stream, x_map, w0_map, w1_map, a), what);
+    return QM_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -462,6 +710,21 @@ int32_t qm_gate_up_swiglu(qm_kv_pool* pool, const uint16_t* x, const uint16_t* g
     const Segment seg{gate_weight, nullptr, out, intermediate};
     return run_gemm<EPI_SWIGLU>(x, &seg, 1, up_weight, nullptr, rows, hidden, pool->status_dev,
                                 static_cast<cudaStream_t>(stream), "fused gate/up/SwiGLU launch");
+}
+
+int32_t qm_linear_rows(qm_kv_pool* pool, const uint16_t* x, const uint16_t* weight, const uint16_t* bias,
+                       const uint16_t* residual, uint16_t* out, int32_t rows, int32_t out_features, int32_t in_features,
+                       void* stream) {
+    if (!pool) return qm_fail(QM_EINVAL, "pool is null");
+    return run_rows_gemm<false>(x, weight, nullptr, bias, residual, out, rows, out_features, in_features, pool->status_dev,
+                                static_cast<cudaStream_t>(stream), "many-row projection launch");
+}
+
+int32_t qm_gate_up_swiglu_rows(qm_kv_pool* pool, const uint16_t* x, const uint16_t* gate_weight, const uint16_t* up_weight,
+                               uint16_t* out, int32_t rows, int32_t hidden, int32_t intermediate, void* stream) {
+    if (!pool) return qm_fail(QM_EINVAL, "pool is null");
+    return run_rows_gemm<true>(x, gate_weight, up_weight, nullptr, nullptr, out, rows, intermediate, hidden, pool->status_dev,
+                               static_cast<cudaStream_t>(stream), "many-row gate/up/SwiGLU launch");
 }
 
 }  // extern "C"

@@ -156,6 +156,20 @@ public:
               "Qingming fused gate/up/SwiGLU launch");
     }
 
+    // linear_generic of the prefill loop (17.cu:16730-16860) for `rows` token rows; `residual` folds the loop's
+    // launch_add into the same launch.
+    void linear_generic(const uint16_t* input, const uint16_t* weight, const uint16_t* bias, const uint16_t* residual,
+                        uint16_t* output, int rows, int output_columns, int reduction_columns) {
+        check(qm_linear_rows(pool_, input, weight, bias, residual, output, rows, output_columns, reduction_columns, stream_),
+              "Qingming generic linear launch");
+    }
+    // The prefill loop's gate and up projections plus launch_swiglu (17.cu:16833-16860) in one launch.
+    void gate_up_swiglu_rows(const uint16_t* input, const uint16_t* gate_w, const uint16_t* up_w, uint16_t* output, int rows,
+                             int hidden, int intermediate) {
+        check(qm_gate_up_swiglu_rows(pool_, input, gate_w, up_w, output, rows, hidden, intermediate, stream_),
+              "Qingming prefill gate/up/SwiGLU launch");
+    }
+
     // NativeFinalHead::run_fast_device after the head projection (17.cu:14475-14560) for every stream at once:
     // cast, repetition penalty, token suppression, greedy argmax (top_k = 0) or top-k sampling, history record.
     void final_head_sample(const uint16_t* logits, int batch, int vocab, int32_t* history, int history_capacity,
