@@ -544,9 +544,13 @@ qm_rows_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_cons
                 const int buf = local & 1;
                 if (!mbar_wait_bounded(acc_empty(buf), ((local >> 1) & 1) ^ 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
                 tc_fence_after();
+                // The next stage's barrier is probed before this stage's MMAs are issued, so that the probe's
+                // shared-memory round trip (about 190 cycles) overlaps the issue instead of draining the pipe.
+                uint32_t seen = mbar_probe(full_bar(it % kRowsStages), (it / kRowsStages) & 1);
                 for (int kc = 0; kc < a.k_chunks; ++kc, ++it) {
                     const int st = it % kRowsStages;
-                    if (!mbar_wait_bounded(full_bar(st), (it / kRowsStages) & 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                    if (!mbar_wait_probed(seen, full_bar(st), (it / kRowsStages) & 1, dead)) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
+                    seen = kc + 1 < a.k_chunks ? mbar_probe(full_bar((it + 1) % kRowsStages), ((it + 1) / kRowsStages) & 1) : 0u;
                     tc_fence_after();
                     const uint32_t xa = sbase + RowsSmem::kRing + st * kRowsStageBytes;
                     const uint32_t wa = xa + kRowsStageA;
