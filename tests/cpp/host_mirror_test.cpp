@@ -17,6 +17,7 @@ void qmo_append(const uint16_t*, const uint16_t*, const uint16_t*, const uint16_
 int qmo_decode_attention_batch(const uint16_t*, const uint16_t* const*, const uint16_t* const*, const int32_t*,
                                const int32_t*, int, int, int, int, uint16_t*, float*);
 float qmo_bf16_to_f32(uint16_t);
+void qmo_linear(const uint16_t*, const uint16_t*, const uint16_t*, const uint16_t*, int, int, int, int, uint16_t*);
 int qmo_final_head_sample(const uint16_t*, int, int32_t*, int, int, int, int, int, int, float, uint64_t*, float*);
 }
 
@@ -112,6 +113,27 @@ int main() {
         if (code != want_code || recorded != want_code) { std::printf("final head: code %d, oracle %d, recorded %d\n", code, want_code, recorded); return 5; }
         for (int i = 0; i < hidden; ++i)
             if (row[i] != table_rows[(size_t)code * hidden + i]) { std::printf("embedding row differs at %d\n", i); return 6; }
+
+        // the prefill loop's generic linear with its residual add, for more rows than one tile holds
+        const int prows = 200, pin = 128, pout = 192;
+        std::vector<uint16_t> px((size_t)prows * pin), pw((size_t)pout * pin), pb(pout), pres((size_t)prows * pout), pwant((size_t)prows * pout),
+            pgot((size_t)prows * pout);
+        qmo_fill_normal_bf16(31, px.data(), (int64_t)px.size());
+        qmo_fill_normal_bf16(32, pw.data(), (int64_t)pw.size());
+        qmo_fill_normal_bf16(33, pb.data(), (int64_t)pb.size());
+        qmo_fill_normal_bf16(34, pres.data(), (int64_t)pres.size());
+        qmo_linear(px.data(), pw.data(), pb.data(), pres.data(), prows, pout, pin, 1, pwant.data());
+        qm::DeviceBuffer dpx, dpw, dpb, dpres, dpout(pgot.size() * 2);
+        upload(px, dpx); upload(pw, dpw); upload(pb, dpb); upload(pres, dpres);
+        engine.linear_generic(dpx.as<uint16_t>(), dpw.as<uint16_t>(), dpb.as<uint16_t>(), dpres.as<uint16_t>(), dpout.as<uint16_t>(),
+                              prows, pout, pin);
+        cudaStreamSynchronize(stream);
+        cudaMemcpy(pgot.data(), dpout.pointer, pgot.size() * 2, cudaMemcpyDeviceToHost);
+        double worst = 0.0;
+        for (size_t i = 0; i < pgot.size(); ++i)
+            worst = std::fmax(worst, std::fabs((double)qmo_bf16_to_f32(pgot[i]) - (double)qmo_bf16_to_f32(pwant[i])));
+        // unit-variance operands: outputs of magnitude up to ~50, one bf16 ulp there is 0.25
+        if (!(worst <= 0.26)) { std::printf("generic linear: worst difference %g\n", worst); return 7; }
     } catch (const std::exception& e) {
         std::printf("exception: %s\n", e.what());
         return 1;
