@@ -60,14 +60,82 @@ __global__ void __launch_bounds__(kNormThreads) qm_rmsnorm_rows_kernel(const uin
     }
 }
 
+// bf16(lo) | bf16(hi) << 16 with the reference's rounding: one cvt.rn.bf16x2 for finite values and infinities,
+// where it equals the integer rounding bit for bit; a NaN takes the integer path so that its payload matches too.
+__device__ __forceinline__ uint32_t round_pair(float lo, float hi) {
+    if (lo != lo || hi != hi) return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
+    return pack_bf16x2(lo, hi);
+}
+
+// The same arithmetic with 16-byte global accesses and packed roundings.  The row (or hidden + x) is staged in
+// shared memory by vector loads and each thread then reads ITS columns t, t + 256, ... from there, so the
+// accumulation order and with it every output bit stay those of the kernel above; the normalised row leaves as
+// 16-byte stores.  Needs dim % 8 == 0 and 16-byte aligned tensors.
+__global__ void __launch_bounds__(kNormThreads) qm_rmsnorm_rows_vec_kernel(const uint16_t* __restrict__ x,
+                                                                          const uint16_t* __restrict__ hidden,
+                                                                          const uint16_t* __restrict__ weight,
+                                                                          uint16_t* __restrict__ residual,
+                                                                          uint16_t* __restrict__ normalized, int dim,
+                                                                          float epsilon) {
+    extern __shared__ uint4 row_vectors[];
+    __shared__ float warp_values[8];
+    pdl_trigger();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * dim;
+    const int vectors = dim >> 3;
+    for (int v = threadIdx.x; v < vectors; v += kNormThreads) {
+        uint4 raw = *reinterpret_cast<const uint4*>(x + base + 8 * v);
+        if (hidden) {
+            const uint4 h = *reinterpret_cast<const uint4*>(hidden + base + 8 * v);
+            uint32_t* rw = reinterpret_cast<uint32_t*>(&raw);
+            const uint32_t* hw = reinterpret_cast<const uint32_t*>(&h);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                rw[i] = round_pair(__fadd_rn(bf16_lo(hw[i]), bf16_lo(rw[i])), __fadd_rn(bf16_hi(hw[i]), bf16_hi(rw[i])));
+            *reinterpret_cast<uint4*>(residual + base + 8 * v) = raw;
+        }
+        row_vectors[v] = raw;
+    }
+    __syncthreads();
+    const uint16_t* row_values = reinterpret_cast<const uint16_t*>(row_vectors);
+    float local = 0.0f;
+    for (int c = threadIdx.x; c < dim; c += kNormThreads) {
+        const float v = bf16_bits_to_f32(row_values[c]);
+        local = fmaf(v, v, local);
+    }
+    const float sum = block_sum_reference_order(local, warp_values);
+    const float inverse_rms = rsqrtf(__fadd_rn(__fdiv_rn(sum, (float)dim), epsilon));
+    for (int v = threadIdx.x; v < vectors; v += kNormThreads) {
+        const uint4 raw = row_vectors[v];
+        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(weight + 8 * v));
+        const uint32_t* rw = reinterpret_cast<const uint32_t*>(&raw);
+        const uint32_t* ww = reinterpret_cast<const uint32_t*>(&wv);
+        uint4 outv;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&outv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t n = round_pair(__fmul_rn(bf16_lo(rw[i]), inverse_rms), __fmul_rn(bf16_hi(rw[i]), inverse_rms));
+            ow[i] = round_pair(__fmul_rn(bf16_lo(n), bf16_lo(ww[i])), __fmul_rn(bf16_hi(n), bf16_hi(ww[i])));
+        }
+        *reinterpret_cast<uint4*>(normalized + base + 8 * v) = outv;
+    }
+}
+
 int32_t launch_norm(const uint16_t* x, const uint16_t* hidden, const uint16_t* weight, uint16_t* residual,
                     uint16_t* normalized, int rows, int dim, float epsilon, cudaStream_t stream, const char* what) {
     if (!x || !weight || !normalized) return qm_fail(QM_EINVAL, "null tensor pointer");
     if (rows < 0 || dim < 1 || dim > 24 * 1024) return qm_fail(QM_EINVAL, "invalid geometry");
     if (rows == 0) return QM_OK;
-    QM_CUDA_TRY(qm_launch(qm_rmsnorm_rows_kernel, dim3(rows), dim3(kNormThreads), (size_t)dim * sizeof(uint16_t), stream, x,
-                          hidden, weight, residual, normalized, dim, epsilon),
-                what);
+    const uintptr_t all = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(weight) |
+                          reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(normalized);
+    if (dim % 8 == 0 && (all & 15u) == 0)
+        QM_CUDA_TRY(qm_launch(qm_rmsnorm_rows_vec_kernel, dim3(rows), dim3(kNormThreads), (size_t)dim * sizeof(uint16_t), stream, x,
+                              hidden, weight, residual, normalized, dim, epsilon),
+                    what);
+    else
+        QM_CUDA_TRY(qm_launch(qm_rmsnorm_rows_kernel, dim3(rows), dim3(kNormThreads), (size_t)dim * sizeof(uint16_t), stream, x,
+                              hidden, weight, residual, normalized, dim, epsilon),
+                    what);
     return QM_OK;
 }
 

@@ -57,6 +57,39 @@ def test_norm_kernels_match_the_bit_faithful_oracle(qm, name):
         eng.close()
 
 
+@pytest.mark.parametrize("rows,dim", [(5, 2048), (300, 1024), (3, 4104)])
+def test_vector_and_scalar_norm_paths_give_the_same_bits(qm, rows, dim):
+    """16-byte aligned rows take the vector kernel, a view shifted by one element the scalar one: same bits."""
+    import torch
+
+    x = oracle.normal_bf16(201 + rows, (rows, dim))
+    h = oracle.normal_bf16(202 + rows, (rows, dim))
+    x[0, 5] = 0x7f80          # +inf: the row's outputs become NaN / 0 exactly as in the scalar kernel
+    x[1, 7] = 0x7fc1          # a NaN with a payload
+    h[2, 9] = 0xff80          # -inf in the residual branch only
+    w = oracle.scaled_normal_bf16(203, (dim,), 0.5)
+    eng = engine(qm)
+    try:
+        def shifted(bits):
+            flat = torch.zeros(bits.size + 1, dtype=torch.bfloat16, device="cuda")
+            view = flat[1:].view(bits.shape)
+            view.copy_(dev(bits))
+            return view
+
+        aligned = scenario._bits(eng.launch_rmsnorm(dev(x), dev(w)))
+        unaligned = scenario._bits(eng.launch_rmsnorm(shifted(x), dev(w), out=shifted(x)))
+        assert np.array_equal(aligned, unaligned)
+        res_a, nrm_a = eng.launch_add_postnorm_m1(dev(h), dev(x), dev(w))
+        res_u, nrm_u = eng.launch_add_postnorm_m1(shifted(h), shifted(x), dev(w), residual=shifted(x), normalized=shifted(x))
+        torch.cuda.synchronize()
+        assert np.array_equal(scenario._bits(res_a), scenario._bits(res_u))
+        assert np.array_equal(scenario._bits(nrm_a), scenario._bits(nrm_u))
+        if rows > 3:      # the rows without non-finite values, against the bit-faithful oracle
+            nearly_identical(aligned[3:], oracle.rmsnorm(x, w)[3:])
+    finally:
+        eng.close()
+
+
 @pytest.mark.parametrize("rows,out_features,in_features", [(3, 384, 2048), (33, 384, 2048), (32, 4096, 2048),
                                                            (64, 2048, 6144), (1, 100, 64), (17, 3072, 2048)])
 def test_projection_matches_double_precision_oracle(qm, rows, out_features, in_features):
