@@ -331,6 +331,27 @@ def ref_gate_up_swiglu(x, gate_w, up_w):
     return out
 
 
+def ref_linear_generic(x, w, bias=None, residual=None):
+    """The reference's native_ops::linear_bf16 (+ code_predictor::launch_add) for all rows at once, on a GPU."""
+    x, w = _u16(x), _u16(w)
+    out = np.empty((x.shape[0], w.shape[0]), dtype=np.uint16)
+    rc = ref().qmref_linear_generic(_p(x), _p(w), _p(_u16(bias)) if bias is not None else None,
+                                    _p(_u16(residual)) if residual is not None else None, _p(out), c_int(x.shape[0]),
+                                    c_int(w.shape[0]), c_int(x.shape[1]))
+    assert rc == 0, rc
+    return out
+
+
+def ref_gate_up_swiglu_generic(x, gate_w, up_w):
+    """The reference's two linear_bf16 calls and code_predictor::launch_swiglu for all rows at once, on a GPU."""
+    x, gate_w, up_w = _u16(x), _u16(gate_w), _u16(up_w)
+    out = np.empty((x.shape[0], gate_w.shape[0]), dtype=np.uint16)
+    rc = ref().qmref_gate_up_swiglu_generic(_p(x), _p(gate_w), _p(up_w), _p(out), c_int(x.shape[0]), c_int(x.shape[1]),
+                                            c_int(gate_w.shape[0]))
+    assert rc == 0, rc
+    return out
+
+
 def final_head_sample(logits, history=None, generation_index=0, flags=0, eos_token=2150, reserved_begin=None, top_k=0,
                       temperature=0.9, rng_state=0):
     """One stream through the restated final-head chain.  Returns (code, processed scores, new rng state, history)."""

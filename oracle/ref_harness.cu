@@ -279,6 +279,54 @@ int qmref_gate_up_swiglu_rows(const uint16_t* x, const uint16_t* gate_w, const u
     return 0;
 }
 
+// The prefill loop's projections (17.cu:16730-16880): native_ops::linear_bf16 for `rows` token rows at once, and
+// code_predictor::launch_add for the residual sum that follows the o- and down-projections.
+int qmref_linear_generic(const uint16_t* x, const uint16_t* weight, const uint16_t* bias, const uint16_t* residual,
+                         uint16_t* out, int rows, int n_dim, int k_dim) {
+    DevBuf dx, dw, db, dr, dout;
+    RH_CHECK(dx.alloc((size_t)rows * k_dim * 2)); RH_CHECK(dw.alloc((size_t)n_dim * k_dim * 2));
+    RH_CHECK(db.alloc((size_t)n_dim * 2)); RH_CHECK(dr.alloc((size_t)rows * n_dim * 2)); RH_CHECK(dout.alloc((size_t)rows * n_dim * 2));
+    RH_CHECK(cudaMemcpy(dx.p, x, dx.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dw.p, weight, dw.bytes, cudaMemcpyHostToDevice));
+    if (bias) RH_CHECK(cudaMemcpy(db.p, bias, db.bytes, cudaMemcpyHostToDevice));
+    if (residual) RH_CHECK(cudaMemcpy(dr.p, residual, dr.bytes, cudaMemcpyHostToDevice));
+    try {
+        qwen3_tts::native_ops::linear_bf16(dx.as<uint16_t>(), dw.as<uint16_t>(), bias ? db.as<uint16_t>() : (uint16_t*)nullptr,
+                                           dout.as<uint16_t>(), rows, n_dim, k_dim, nullptr);
+        if (residual) rp::launch_add(dr.as<uint16_t>(), dout.as<uint16_t>(), dout.as<uint16_t>(), (uint64_t)rows * n_dim, nullptr);
+    } catch (const std::exception&) {
+        return 1;
+    }
+    RH_CHECK(cudaGetLastError());
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(out, dout.p, dout.bytes, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+// The prefill loop's gate and up projections (linear_bf16 twice) followed by code_predictor::launch_swiglu.
+int qmref_gate_up_swiglu_generic(const uint16_t* x, const uint16_t* gate_w, const uint16_t* up_w, uint16_t* out, int rows,
+                                 int hidden, int intermediate) {
+    DevBuf dx, dg, du, dgate, dup, dout;
+    const size_t out_bytes = (size_t)rows * intermediate * 2;
+    RH_CHECK(dx.alloc((size_t)rows * hidden * 2)); RH_CHECK(dg.alloc((size_t)intermediate * hidden * 2));
+    RH_CHECK(du.alloc((size_t)intermediate * hidden * 2)); RH_CHECK(dgate.alloc(out_bytes)); RH_CHECK(dup.alloc(out_bytes));
+    RH_CHECK(dout.alloc(out_bytes));
+    RH_CHECK(cudaMemcpy(dx.p, x, dx.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dg.p, gate_w, dg.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(du.p, up_w, du.bytes, cudaMemcpyHostToDevice));
+    try {
+        qwen3_tts::native_ops::linear_bf16(dx.as<uint16_t>(), dg.as<uint16_t>(), nullptr, dgate.as<uint16_t>(), rows, intermediate, hidden, nullptr);
+        qwen3_tts::native_ops::linear_bf16(dx.as<uint16_t>(), du.as<uint16_t>(), nullptr, dup.as<uint16_t>(), rows, intermediate, hidden, nullptr);
+        rp::launch_swiglu(dgate.as<uint16_t>(), dup.as<uint16_t>(), dout.as<uint16_t>(), (uint64_t)rows * intermediate, nullptr);
+    } catch (const std::exception&) {
+        return 1;
+    }
+    RH_CHECK(cudaGetLastError());
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(out, dout.p, dout.bytes, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
 // The reference's final-head chain for one stream, as NativeFinalHead::run_fast strings it together:
 // cast_final_head_logits, repetition_penalty (flag 1), suppress_tokens (flag 2), then argmax_final_head
 // (top_k <= 0) or gpu_sample_topk_f32_kernel, then record_sampled_code_kernel (flag 4).  The vocabulary is the

@@ -6,6 +6,7 @@ import numpy as np
 import pytest
 
 from oracle import qm_oracle as oracle
+import prefill_projection_cases as cases
 import scenario
 
 pytestmark = pytest.mark.gpu
@@ -70,6 +71,31 @@ def test_gate_up_swiglu_rows_matches_double_precision_oracle(qm, rows, hidden, i
         # millions of outputs: allow the one-ulp flip of the largest bf16 outputs (an ulp is 2^-7 of the value or less)
         largest = float(np.max(np.abs(oracle.bf16_to_f32(want))))
         close(got, want, scale=max(1.0, largest * 2.0 ** -7 / TOL_MAX_ABS))
+    finally:
+        eng.close()
+
+
+@pytest.mark.parametrize("name", sorted(cases.CASES))
+def test_against_reference_prefill_kernel_outputs(qm, name):
+    """The reference's own linear_bf16 / launch_add / launch_swiglu outputs on the same inputs (golden file made on a
+    B200): the tensor-core accumulation order differs from the reference's 32-lane sums, so the comparison is the
+    bf16 tolerance, and the fraction of outputs that differ at all stays small."""
+    import torch
+    from pathlib import Path
+
+    golden = np.load(Path(__file__).resolve().parent / "golden" / "reference_prefill_projection_golden.npz")
+    c = cases.ProjectionCase(*cases.CASES[name])
+    eng = engine(qm)
+    try:
+        plain = scenario._bits(eng.linear_generic(dev(c.x), dev(c.w)))
+        full = scenario._bits(eng.linear_generic(dev(c.x), dev(c.w), dev(c.bias), dev(c.residual)))
+        act = scenario._bits(eng.gate_up_swiglu_rows(dev(c.x), dev(c.w), dev(c.up_w)))
+        torch.cuda.synchronize()
+        assert eng.status() == 0
+        for got, key in ((plain, "linear"), (full, "linear_bias_residual"), (act, "swiglu")):
+            want = golden[f"{name}_{key}"]
+            close(got, want, scale=2.0)
+            assert (got != want).mean() <= 5e-3, (key, (got != want).mean())
     finally:
         eng.close()
 
