@@ -5,6 +5,8 @@
 // are added in the same order with xor shuffles (float addition commutes, so a + b from either side is equal).
 #pragma once
 
+#include <math_constants.h>
+
 #include "qm_common.cuh"
 
 __device__ __forceinline__ float reference_order_sum_of_squares(float s0, float s1, float s2, float s3) {
@@ -23,48 +25,55 @@ __device__ __forceinline__ float reference_order_sum_of_squares(float s0, float 
     s3 += __shfl_xor_sync(0xffffffffu, s3, 1);
     s0 = __fadd_rn(s0, s2);
     s1 = __fadd_rn(s1, s3);
-    const float warp_sum = __fadd_rn(s0, s1);      // exact in lanes 0, 8, 16, 24
-    const float w0 = __shfl_sync(0xffffffffu, warp_sum, 0);
-    const float w1 = __shfl_sync(0xffffffffu, warp_sum, 8);
-    const float w2 = __shfl_sync(0xffffffffu, warp_sum, 16);
-    const float w3 = __shfl_sync(0xffffffffu, warp_sum, 24);
-    return __fadd_rn(__fadd_rn(w0, w2), __fadd_rn(w1, w3));
+    // Every lane of 8-lane group j now holds w_j, the sum of reference warp j: the butterflies above add the same
+    // pairs in every lane, only with the operands of some additions swapped.  (w0 + w2) + (w1 + w3) likewise:
+    // xor 16 pairs group j with j ^ 2, xor 8 then pairs the two partial sums.
+    const float warp_sum = __fadd_rn(s0, s1);
+    const float pair_sum = __fadd_rn(warp_sum, __shfl_xor_sync(0xffffffffu, warp_sum, 16));
+    return __fadd_rn(pair_sum, __shfl_xor_sync(0xffffffffu, pair_sum, 8));
 }
 
-// kHardwareRounding: round with cvt.rn.bf16 (one instruction; identical to the reference's integer rounding for
-// every finite value and infinity, different NaN payload).  The caller picks the integer path when a row holds a
-// non-finite input, so NaN bits also match the reference.
-template <bool kHardwareRounding>
-__device__ __forceinline__ float rope_round(float v) {
-    if (kHardwareRounding) return __bfloat162float(__float2bfloat16_rn(v));
-    return round_bf16(v);
-}
-
-template <bool kHardwareRounding>
-__device__ __forceinline__ uint2 norm_rope_row_impl(const float (&x)[4], const float (&w)[4], const float (&c)[4],
-                                                    const float (&s)[4], int lane, float epsilon) {
-    const float sum = reference_order_sum_of_squares(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]),
-                                                     __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
-    // sum / 128 is exact as a multiplication by 2^-7
-    const float inverse_rms = rsqrtf(__fadd_rn(__fmul_rn(sum, 1.0f / (float)kHeadDim), epsilon));
-    // RMSNorm: normalise in fp32 -> bf16 -> multiply by the bf16 weight -> bf16.
+// The rest of a row once its sum of squares is known, integer rounding throughout (any input): the reference's
+// arithmetic spelled out value by value.
+__device__ __forceinline__ uint2 norm_rope_row_exact(const float (&x)[4], const float (&w)[4], const float (&c)[4],
+                                                     const float (&s)[4], int lane, float inverse_rms) {
     float n[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-        n[i] = rope_round<kHardwareRounding>(__fmul_rn(rope_round<kHardwareRounding>(__fmul_rn(x[i], inverse_rms)), w[i]));
-    // rotate_half: dimension d pairs with d +- 64, which lane l ^ 16 holds.
+    for (int i = 0; i < 4; ++i) n[i] = round_bf16(__fmul_rn(round_bf16(__fmul_rn(x[i], inverse_rms)), w[i]));
     float y[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
+        // rotate_half: dimension d pairs with d +- 64, which lane l ^ 16 holds.
         float partner = __shfl_xor_sync(0xffffffffu, n[i], 16);
         if (lane < 16) partner = -partner;
-        const float first = rope_round<kHardwareRounding>(__fmul_rn(n[i], c[i]));
-        const float second = rope_round<kHardwareRounding>(__fmul_rn(partner, s[i]));
+        const float first = round_bf16(__fmul_rn(n[i], c[i]));
+        const float second = round_bf16(__fmul_rn(partner, s[i]));
         y[i] = __fadd_rn(first, second);
     }
-    if (kHardwareRounding) return make_uint2(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]));
     return make_uint2(f32_to_bf16_bits(y[0]) | (f32_to_bf16_bits(y[1]) << 16),
                       f32_to_bf16_bits(y[2]) | (f32_to_bf16_bits(y[3]) << 16));
+}
+
+// The same for rows whose values are all finite, two values per instruction: cvt.rn.bf16x2 rounds a pair (equal
+// to the integer rounding for every finite value), the partner values travel as two packed words instead of four
+// floats, and the sign of rotate_half is folded into the sine ((-a) * b and a * (-b) are the same bits).
+__device__ __forceinline__ uint2 norm_rope_row_packed(const float (&x)[4], const float (&w)[4], const float (&c)[4],
+                                                      const float (&s)[4], int lane, float inverse_rms) {
+    const uint32_t a01 = pack_bf16x2(__fmul_rn(x[0], inverse_rms), __fmul_rn(x[1], inverse_rms));
+    const uint32_t a23 = pack_bf16x2(__fmul_rn(x[2], inverse_rms), __fmul_rn(x[3], inverse_rms));
+    const uint32_t n01 = pack_bf16x2(__fmul_rn(bf16_lo(a01), w[0]), __fmul_rn(bf16_hi(a01), w[1]));
+    const uint32_t n23 = pack_bf16x2(__fmul_rn(bf16_lo(a23), w[2]), __fmul_rn(bf16_hi(a23), w[3]));
+    const uint32_t p01 = __shfl_xor_sync(0xffffffffu, n01, 16);
+    const uint32_t p23 = __shfl_xor_sync(0xffffffffu, n23, 16);
+    const bool low_half = lane < 16;
+    const float s0 = low_half ? -s[0] : s[0], s1 = low_half ? -s[1] : s[1];
+    const float s2 = low_half ? -s[2] : s[2], s3 = low_half ? -s[3] : s[3];
+    const uint32_t f01 = pack_bf16x2(__fmul_rn(bf16_lo(n01), c[0]), __fmul_rn(bf16_hi(n01), c[1]));
+    const uint32_t f23 = pack_bf16x2(__fmul_rn(bf16_lo(n23), c[2]), __fmul_rn(bf16_hi(n23), c[3]));
+    const uint32_t g01 = pack_bf16x2(__fmul_rn(bf16_lo(p01), s0), __fmul_rn(bf16_hi(p01), s1));
+    const uint32_t g23 = pack_bf16x2(__fmul_rn(bf16_lo(p23), s2), __fmul_rn(bf16_hi(p23), s3));
+    return make_uint2(pack_bf16x2(__fadd_rn(bf16_lo(f01), bf16_lo(g01)), __fadd_rn(bf16_hi(f01), bf16_hi(g01))),
+                      pack_bf16x2(__fadd_rn(bf16_lo(f23), bf16_lo(g23)), __fadd_rn(bf16_hi(f23), bf16_hi(g23))));
 }
 
 // One row: raw = 4 packed bf16 of this lane; returns the normed + roped row, packed.
@@ -72,9 +81,12 @@ __device__ __forceinline__ uint2 norm_rope_row(uint2 raw, uint2 wraw, const floa
                                                float epsilon) {
     const float x[4] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y)};
     const float w[4] = {bf16_lo(wraw.x), bf16_hi(wraw.x), bf16_lo(wraw.y), bf16_hi(wraw.y)};
-    // exponent all ones <=> inf or NaN, for any of the four inputs of any lane
-    const bool odd = ((raw.x & 0x7f80u) == 0x7f80u) || ((raw.x & 0x7f800000u) == 0x7f800000u) ||
-                     ((raw.y & 0x7f80u) == 0x7f80u) || ((raw.y & 0x7f800000u) == 0x7f800000u);
-    if (__any_sync(0xffffffffu, odd)) return norm_rope_row_impl<false>(x, w, c, s, lane, epsilon);
-    return norm_rope_row_impl<true>(x, w, c, s, lane, epsilon);
+    const float sum = reference_order_sum_of_squares(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]),
+                                                     __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
+    // sum / 128 is exact as a multiplication by 2^-7
+    const float inverse_rms = rsqrtf(__fadd_rn(__fmul_rn(sum, 1.0f / (float)kHeadDim), epsilon));
+    // An infinite or NaN input makes the sum (the same value in every lane) infinite or NaN; so does a finite
+    // input whose square overflows.  Those rows take the integer-rounding path, whose NaN bits are the reference's.
+    if (!(sum < CUDART_INF_F)) return norm_rope_row_exact(x, w, c, s, lane, inverse_rms);
+    return norm_rope_row_packed(x, w, c, s, lane, inverse_rms);
 }
