@@ -9,6 +9,7 @@ bf16 tensors are numpy uint16 arrays holding the raw bits.
 from __future__ import annotations
 
 import ctypes
+import os
 import subprocess
 from ctypes import POINTER, c_double, c_float, c_int, c_int32, c_int64, c_uint16, c_uint64, c_void_p
 from pathlib import Path
@@ -28,8 +29,9 @@ _ref = None
 def build(with_reference: bool = False) -> None:
     """Compiles the C restatement (and, where the reference checkout exists, the harness)."""
     subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
-    if with_reference and Path("/root/reference/devices/rtx4090-24g/qwen3_tts_1_7b.cu").exists():
-        subprocess.run(["make", "-C", str(HERE), "ref"], check=True, capture_output=True)
+    reference_dir = os.environ.get("QM_REFERENCE_DIR", "/root/reference")      # the reference checkout, read-only
+    if with_reference and (Path(reference_dir) / "devices" / "rtx4090-24g" / "qwen3_tts_1_7b.cu").exists():
+        subprocess.run(["make", "-C", str(HERE), "ref", f"REFERENCE_DIR={reference_dir}"], check=True, capture_output=True)
 
 
 def lib() -> ctypes.CDLL:
