@@ -269,10 +269,13 @@ def run_ours(args):
     # host memory, inside the timed region.  Copies are issued per chunk of layers on their own streams so that
     # the transfer of one chunk overlaps the kernels of another, as a serving loop would do; every copy and kernel
     # of the K timed steps still lies between the two timing events.
-    # The first chunk is a single layer, so that only a small copy stands before the step's first kernel.
-    if LAYERS >= 6:
-        rest = 4
-        bounds = [0] + [1 + (LAYERS - 1) * c // rest for c in range(rest + 1)]
+    # Chunk sizes grow from one layer (so that only a small copy stands before the step's first kernel, and the
+    # copy of a chunk is finished before the kernels of the chunks ahead of it are) and shrink again towards the
+    # end (so that only a small read-back is left when the last kernel ends).
+    if LAYERS >= 16:
+        bounds = sorted({0, 1, 3, 8, LAYERS // 2 + 4, LAYERS - 4, LAYERS - 1, LAYERS})
+    elif LAYERS >= 6:
+        bounds = [0, 1, LAYERS // 2, LAYERS - 1, LAYERS]
     else:
         bounds = [0, LAYERS]
     n_chunks = len(bounds) - 1
@@ -403,7 +406,7 @@ def run_ours(args):
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                 "ms_per_step": e2e_ms / args.steps,
                 "note": "every layer's q/k/v copied from pinned host memory and every context copied back inside the "
-                        "timed region, in chunks of layers (the first a single layer) on copy streams so transfers overlap kernels, the last read-back overlapping the next step's first kernels; the KV "
+                        "timed region, in chunks of layers (small at both ends of the step) on copy streams so transfers overlap kernels, the last read-back overlapping the next step's first kernels; the KV "
                         "cache is device-resident state by design"},
         "gpu_launches": args.steps * LAYERS,
         "roofline": {"bound": "hbm", "kernel": "qm_decode_splitkv_kernel<fused>", "achieved": achieved,
