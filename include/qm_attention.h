@@ -27,6 +27,7 @@
 #ifndef QM_ATTENTION_H
 #define QM_ATTENTION_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -40,6 +41,7 @@ extern "C" {
 #define QM_ETIMEOUT (-4)   /* a bounded device-side wait gave up                 */
 #define QM_ENOMEM (-5)     /* device allocation failed                           */
 #define QM_EDEVICE (-6)    /* not a compute-capability 10.x device               */
+#define QM_ENCCL (-7)      /* an NCCL call failed or reported an asynchronous error (communicator aborted) */
 
 #define QM_HEAD_DIM 128
 #define QM_PAGE_TOKENS 64
@@ -191,26 +193,35 @@ int32_t qm_decode_step(qm_kv_pool* pool, int32_t layer, const uint16_t* q, const
 /* Decode attention without any allocation, here or in the caller.  No counterpart
  * in the reference, whose engine allocates all workspace at construction.
  * Same inputs, outputs and result as qm_decode_attention, but the scratch
- * lives in a fixed array inside the library (about 1.6 MB of device memory on
+ * lives in a fixed array inside the library (about 1.7 MB of device memory on
  * every GPU that loads the library, held until the process exits).  Meant for
  * hosts that cannot cudaMalloc on this path: a resident serving loop whose
  * device memory was budgeted at start-up and whose second stream (the codec
  * decoder) would be stalled by the device-wide synchronisation an allocation
  * implies, or an engine whose own allocator already holds all device memory.
  *   - at most 64 streams and 8 KV heads per call; more returns QM_ECAPACITY.
- *   - the first call on each device looks up the array's device address (the
- *     pool's device must be current); make that first call before starting
- *     any stream capture.
+ *   - the pool's device must be the current device on every call (QM_EINVAL
+ *     otherwise); the first call on each device looks up the array's device
+ *     address: make that first call before starting any stream capture.
  *   - all calls on a device share the one array and it keeps what the last
  *     call wrote; it starts zeroed and the kernel re-zeroes the counters it
  *     uses, so nothing needs clearing between calls, but two calls
  *     whose kernels overlap on the GPU (different streams, or several
  *     threads) would overwrite each other's partials: issue them on one
  *     stream, or order them with events.
+ *   - a call after which qm_kv_pool_status shows QM_DEVSTAT_TIMEOUT may have
+ *     left arrival counters behind in the array: call
+ *     qm_decode_static_scratch_reset before the next one.
  * Calls no cudaMalloc / cudaFree and no allocating library routine. */
 int32_t qm_decode_attention_static(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot,
                                    const int32_t* seq_lens, const int32_t* page_table, int32_t max_pages,
                                    int32_t batch, int32_t q_heads, uint16_t* out, void* stream);
+
+/* Puts the arrival counters of the library's built-in scratch back to zero on
+ * `stream` (a memset on memory that already exists; allocates nothing).  No
+ * counterpart in the reference.  Needed only after a qm_decode_attention_static
+ * call that reported QM_DEVSTAT_TIMEOUT; the pool's device must be current. */
+int32_t qm_decode_static_scratch_reset(qm_kv_pool* pool, void* stream);
 
 /* Same, but stops before normalisation and returns the partial softmax state
  * of each (stream, query head) over the keys held in THIS pool:
@@ -233,17 +244,88 @@ int32_t qm_attention_combine(const float* partials, int32_t parts, int32_t rows,
 
 /* Exchange + combine in one kernel over peer memory, for streams whose keys are split across the GPUs of one box.
  * No counterpart in the reference (single GPU).  Every rank calls it at the same point of its stream with its own
- * partials (from qm_decode_attention_partial); the kernel stores them into every rank's exchange buffer with plain
- * peer-to-peer stores, waits - bounded, QM_DEVSTAT_TIMEOUT if a rank never shows up - until all ranks' rows of
- * this call have arrived in its own buffer, and folds them in rank order into out [rows][128] bf16.
+ * partials (from qm_decode_attention_partial) and the same `rows`; the kernel stores them into every rank's exchange
+ * buffer with plain peer-to-peer stores, waits - bounded, QM_DEVSTAT_TIMEOUT if a rank never shows up - until all
+ * ranks' copies of each row of this call have arrived in its own buffer, and folds them in rank order into
+ * out [rows][128] bf16 (the order and arithmetic of qm_attention_combine: every rank ends with the same bits).
  *   peer_buffers_dev: DEVICE array of `world` pointers, entry r = rank r's exchange buffer mapped into this
- *     process (symmetric / IPC memory), each of qm_exchange_buffer_bytes(world, rows_capacity) bytes, zero-filled
- *     once when allocated and never touched by the host afterwards;
- *   epoch: 1 for the first call on these buffers, then 2, 3, ... - the same on every rank. */
+ *     process (symmetric / IPC / peer-enabled memory), each of qm_exchange_buffer_bytes(world, rows_capacity) bytes,
+ *     zero-filled once when allocated and never touched by the host afterwards.
+ * The call number lives in the buffer (one counter per row, advanced by the kernel), so consecutive calls need no
+ * host-side bookkeeping, `rows` may differ from call to call (as long as every rank passes the same value), and a
+ * launch captured in a CUDA graph can be replayed.  After a call that reported QM_DEVSTAT_TIMEOUT the ranks'
+ * counters may disagree: zero every rank's buffer again (all ranks, with a host barrier) before the next call.
+ * rows beyond what the GPU can hold resident at once (about 1 700 on B200) are rejected with QM_ECAPACITY. */
 int64_t qm_exchange_buffer_bytes(int32_t world, int32_t rows_capacity);
 int32_t qm_attention_exchange_combine(qm_kv_pool* pool, const float* local_partials, void* const* peer_buffers_dev,
-                                      int32_t world, int32_t rank, int32_t rows, int32_t rows_capacity, uint64_t epoch,
-                                      uint16_t* out, void* stream);
+                                      int32_t world, int32_t rank, int32_t rows, int32_t rows_capacity, uint16_t* out,
+                                      void* stream);
+
+/* The exchange buffers as an object, for hosts that have no symmetric-memory allocator of their own.  No counterpart
+ * in the reference.  qm_exchange_create allocates and zeroes this rank's buffer on the current device.  With one
+ * process per GPU, every rank exports its buffer with qm_exchange_ipc_handle (QM_IPC_HANDLE_BYTES bytes, a CUDA IPC
+ * memory handle), the host passes the handles around by whatever channel it has, and qm_exchange_open_peers maps
+ * the others (`handles` = world consecutive handles in rank order; the own entry is ignored).  With one process
+ * driving several GPUs, qm_exchange_set_peers takes the other ranks' qm_exchange_local_buffer pointers instead
+ * (peer access between the devices must be enabled by the host).  qm_exchange_combine is
+ * qm_attention_exchange_combine on these buffers.  qm_exchange_reset zeroes this rank's buffer on `stream` (after
+ * a timeout; every rank, then a host barrier).  Creation, mapping and destruction allocate and synchronise;
+ * qm_exchange_combine does neither. */
+#define QM_IPC_HANDLE_BYTES 64
+typedef struct qm_exchange qm_exchange;
+int32_t qm_exchange_create(int32_t world, int32_t rank, int32_t rows_capacity, qm_exchange** exchange_out);
+int32_t qm_exchange_destroy(qm_exchange* exchange);
+void* qm_exchange_local_buffer(qm_exchange* exchange);
+int32_t qm_exchange_ipc_handle(qm_exchange* exchange, void* handle_out);
+int32_t qm_exchange_open_peers(qm_exchange* exchange, const void* handles);
+int32_t qm_exchange_set_peers(qm_exchange* exchange, void* const* peer_buffers);
+int32_t qm_exchange_reset(qm_exchange* exchange, void* stream);
+int32_t qm_exchange_combine(qm_kv_pool* pool, qm_exchange* exchange, const float* local_partials, int32_t rows,
+                            uint16_t* out, void* stream);
+
+/* ---- the same exchange through NCCL, for a C++ host with one process or thread per GPU ----
+ * No counterpart in the reference (single GPU; its launch_attention, 17.cu:17895, sees the whole cache). */
+
+/* One layer of decode attention when this pool holds a slice of every stream: the split-KV kernel over the local
+ * keys (qm_decode_attention_partial), ONE ncclAllGather of the [batch][q_heads][130] fp32 partials on `stream`,
+ * and the rank-order combine, so every rank ends with the same bits in out [batch][q_heads][128].
+ *   local_seq_lens[batch]: keys of each stream held in THIS pool (0 is fine)
+ *   partial_send [batch][q_heads][130] fp32, partial_recv [world][batch][q_heads][130] fp32: caller-owned device
+ *     buffers (registering them with NCCL is the caller's choice)
+ *   nccl_comm: the caller's ncclComm_t of `world` ranks; every rank makes the call.
+ * Nothing here allocates or synchronises.  A failed NCCL call returns QM_ENCCL.  A collective that never completes
+ * (a rank that died) is detected by qm_nccl_wait, not here. */
+int32_t qm_decode_attention_sharded(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const int32_t* local_seq_lens,
+                                    const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads,
+                                    uint16_t* out, float* partial_send, float* partial_recv, int32_t world,
+                                    void* workspace, int64_t workspace_bytes, void* nccl_comm, void* stream);
+
+/* Host-side deadline for the collectives queued on `stream`: polls the stream and ncclCommGetAsyncError until the
+ * stream's work is done (QM_OK), NCCL reports an asynchronous error (ncclCommAbort, then QM_ENCCL), the stream
+ * itself fails (abort, QM_ECUDA) or `deadline_ms` passes (abort, QM_ETIMEOUT).  After anything but QM_OK the
+ * communicator is gone and must be rebuilt by the host. */
+int32_t qm_nccl_wait(void* nccl_comm, void* stream, int32_t deadline_ms);
+
+/* The NCCL functions used above.  By default they are resolved at first use from libnccl.so.2 (or the file named
+ * by the environment variable QM_NCCL_LIBRARY); a host that links NCCL itself, or a test that wants to stand in
+ * for it, passes its own table.  Result codes are NCCL's (0 = ncclSuccess, 7 = ncclInProgress); stream_query
+ * returns 0 when the stream has finished, 1 while it is busy, a negative value on error (NULL = cudaStreamQuery).
+ * qm_nccl_set_api(NULL) goes back to the shared library. */
+typedef struct qm_nccl_api {
+    int (*all_gather)(const void* send, void* recv, size_t send_count, int datatype, void* comm, void* stream);
+    int (*comm_get_async_error)(void* comm, int* async_error);
+    int (*comm_abort)(void* comm);
+    int (*comm_count)(const void* comm, int* count);
+    const char* (*get_error_string)(int result);
+    int (*stream_query)(void* stream);
+} qm_nccl_api;
+int32_t qm_nccl_set_api(const qm_nccl_api* api);
+
+/* Convenience for hosts without NCCL plumbing of their own: ncclGetUniqueId (128 bytes), ncclCommInitRank and
+ * ncclCommDestroy through the same lazily loaded library. */
+int32_t qm_nccl_unique_id(void* id_out);
+int32_t qm_nccl_comm_init_rank(void** comm_out, int32_t world, const void* id, int32_t rank);
+int32_t qm_nccl_comm_destroy(void* comm);
 
 /* ---- prefill attention: launch_attention with query_length > 1
  *      (17.cu:17954-17985; kernel talker_attention_kernel :15791-16054) */

@@ -26,11 +26,12 @@ _lib = None
 _ref = None
 
 
-def build(with_reference: bool = False) -> None:
-    """Compiles the C restatement (and, where the reference checkout exists, the harness)."""
+def build(reference_dir=None) -> None:
+    """Compiles the C restatement and, when `reference_dir` (or the environment variable QM_REFERENCE_DIR) names a
+    reference checkout, the harness around the reference's own kernels.  There is no default location."""
     subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
-    reference_dir = os.environ.get("QM_REFERENCE_DIR", "/root/reference")      # the reference checkout, read-only
-    if with_reference and (Path(reference_dir) / "devices" / "rtx4090-24g" / "qwen3_tts_1_7b.cu").exists():
+    reference_dir = reference_dir or os.environ.get("QM_REFERENCE_DIR")
+    if reference_dir and (Path(reference_dir) / "devices" / "rtx4090-24g" / "qwen3_tts_1_7b.cu").exists():
         subprocess.run(["make", "-C", str(HERE), "ref", f"REFERENCE_DIR={reference_dir}"], check=True, capture_output=True)
 
 

@@ -33,6 +33,8 @@ QM_ECUDA = -3
 QM_ETIMEOUT = -4
 QM_ENOMEM = -5
 QM_EDEVICE = -6
+QM_ENCCL = -7
+IPC_HANDLE_BYTES = 64
 QM_SAMPLE_REPETITION, QM_SAMPLE_SUPPRESS, QM_SAMPLE_RECORD = 1, 2, 4
 
 DEVSTAT_BAD_PAGE = 1
@@ -88,7 +90,23 @@ ABI = {
     "qm_embedding_gather": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
     "qm_exchange_buffer_bytes": (c_int64, [c_int32, c_int32]),
     "qm_attention_exchange_combine": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
-                                                ctypes.c_uint64, c_void_p, c_void_p]),
+                                                c_void_p, c_void_p]),
+    "qm_exchange_create": (c_int32, [c_int32, c_int32, c_int32, POINTER(c_void_p)]),
+    "qm_exchange_destroy": (c_int32, [c_void_p]),
+    "qm_exchange_local_buffer": (c_void_p, [c_void_p]),
+    "qm_exchange_ipc_handle": (c_int32, [c_void_p, c_void_p]),
+    "qm_exchange_open_peers": (c_int32, [c_void_p, c_void_p]),
+    "qm_exchange_set_peers": (c_int32, [c_void_p, c_void_p]),
+    "qm_exchange_reset": (c_int32, [c_void_p, c_void_p]),
+    "qm_exchange_combine": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p]),
+    "qm_decode_static_scratch_reset": (c_int32, [c_void_p, c_void_p]),
+    "qm_decode_attention_sharded": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
+                                              c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_void_p]),
+    "qm_nccl_wait": (c_int32, [c_void_p, c_void_p, c_int32]),
+    "qm_nccl_set_api": (c_int32, [c_void_p]),
+    "qm_nccl_unique_id": (c_int32, [c_void_p]),
+    "qm_nccl_comm_init_rank": (c_int32, [POINTER(c_void_p), c_int32, c_void_p, c_int32]),
+    "qm_nccl_comm_destroy": (c_int32, [c_void_p]),
     "qm_prefill_attention_varlen": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
                                               c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
 }

@@ -48,7 +48,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     cmd = [nvcc, *NVCC_FLAGS]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB_PATH), *map(str, sources())]
+    cmd += ["-o", str(LIB_PATH), *map(str, sources()), "-ldl"]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)

@@ -130,6 +130,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
         }
         fence_mbar_init();
     }
+    // Every stage's unit description starts out as a harmless one (segment 0, page 0, no valid keys): a consumer
+    // whose bounded wait gave up reads whatever is there, and these values index shared and global memory.
+    if (tid < 2 * kStages) meta[tid] = (tid & 1) ? make_int4(0, 0, 0, 0) : make_int4(0, 0, 1, 0);
     // ---- Work done before the dependency wait, and kept if it turns out to be right.
     // A CTA of this launch becomes resident as soon as a CTA of the previous kernel retires, often many
     // microseconds before the last one does, and would otherwise sit idle in the wait below while HBM runs dry.
@@ -391,7 +394,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                             *row = norm_rope_row(*row, wq, c, sn, lane, a.epsilon);
                         }
                     }
-                    if (last_page) {
+                    if (last_page && nvalid > 0 && !dead) {      // after a wait that gave up nothing here is trustworthy: no stores
                         const uint2 krow = norm_rope_row(*reinterpret_cast<const uint2*>(staging + 1024 + lane * 8), wk, c, sn,
                                                          lane, a.epsilon);
                         const uint2 vrow = *reinterpret_cast<const uint2*>(staging + 1280 + lane * 8);
@@ -578,8 +581,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                 const float m = qh ? m1 : m0;
                 const bool whole = seg_from_start && page_idx == pages - 1;
                 const size_t row = (size_t)stream * (2 * hkv) + 2 * head + qh;
+                // `dead`: one of this thread's waits gave up (QM_DEVSTAT_TIMEOUT is set).  Its numbers are garbage
+                // and the unit description may be a stale one, so it writes nothing to global memory and takes
+                // no part in the arrival count; the barriers below are still passed by everyone.
                 if (whole) {
-                    if (a.mode == 0) {
+                    if (dead) {
+                    } else if (a.mode == 0) {
                         a.out[row * kHeadDim + d] = (uint16_t)f32_to_bf16_bits(sum / lsum);
                     } else {
                         float* dst = a.partial_out + row * kPartialStride;
@@ -591,10 +598,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                     }
                 } else {
                     float* dst = a.ws_partials + ((size_t)(cta + seg) * 2 + qh) * kPartialStride;
-                    dst[2 + d] = sum;
-                    if (d == 0) {
-                        dst[0] = m;
-                        dst[1] = lsum;
+                    if (!dead) {
+                        dst[2 + d] = sum;
+                        if (d == 0) {
+                            dst[0] = m;
+                            dst[1] = lsum;
+                        }
                     }
                     // Which CTAs hold a part of this segment (unit u belongs to CTA ((u + 1) * G - 1) / U).
                     const long long u_first = (long long)prefix[stream] + (long long)head * pages;
@@ -603,13 +612,16 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                     __threadfence();
                     named_bar_sync(1, kConsumerThreads);
                     if (tid == 0) {
-                        const int arrived = atomicAdd(a.ws_count + seg, 1) + 1;
-                        const int is_last = arrived == c_last - c_first + 1;
-                        if (is_last) a.ws_count[seg] = 0;          // everyone else is done with it
+                        int is_last = 0;
+                        if (!dead) {
+                            const int arrived = atomicAdd(a.ws_count + seg, 1) + 1;
+                            is_last = arrived == c_last - c_first + 1;
+                            if (is_last) a.ws_count[seg] = 0;          // everyone else is done with it
+                        }
                         *fold_flag = is_last;
                     }
                     named_bar_sync(1, kConsumerThreads);
-                    if (*fold_flag) {
+                    if (*fold_flag && !dead) {
                         __threadfence();
                         // Piece i of the segment sits in slot (c_first + i + seg).  The loads of a batch are issued
                         // together (a rolled loop would pay one L2 round trip per piece, twice); the arithmetic stays
@@ -768,7 +780,15 @@ __global__ void __launch_bounds__(kShortThreads) qm_decode_short_kernel(const De
             *reinterpret_cast<const uint2*>(a.q_rot + (row0 + warp) * kHeadDim + 4 * lane);
     }
     if (!mbar_wait_bounded(bar, 0, dead) && lane == 0) atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
-    __syncthreads();
+    if (__syncthreads_or(dead ? 1 : 0)) {
+        // The page never arrived: report it (done above), give the copies one more bounded chance to land so that
+        // none is in flight into this CTA's shared memory when it retires, and write nothing.
+        if (tid == 0) {
+            bool ignore = false;
+            mbar_wait_bounded(bar, 0, ignore);
+        }
+        return;
+    }
 
     // ---- scores in the log2 domain: half-warp per key row, 8 keys per pass over the four warps
     const int half = lane >> 4, lp = lane & 15;
@@ -882,6 +902,12 @@ __global__ void __launch_bounds__(128) qm_combine_partials_kernel(const float* _
 
 size_t partials_bytes(int segments) { return (size_t)(kMaxGrid + segments) * 2 * kPartialStride * sizeof(float); }
 
+// Scratch layout: the per-segment arrival counters come first, at a fixed place (counter i at byte 4 * i, room for
+// the largest launch: kMaxBatchPerLaunch streams of 64 KV heads), the partial slots after them.  A buffer that serves
+// batches of different sizes therefore always finds its counters where the previous call left them at zero, and no
+// partial slot can overlap a counter whatever the grid size is.
+constexpr size_t kCounterRegionBytes = (size_t)kMaxBatchPerLaunch * 64 * sizeof(int32_t);
+
 // Extra inputs of the fused step (append + attention in one launch); null for plain attention.
 struct FusedInputs {
     const uint16_t* k;
@@ -894,15 +920,20 @@ struct FusedInputs {
     float epsilon;
 };
 
-// Units per CTA to prefetch into L2 ahead of the dependency wait.  QM_DECODE_PREFETCH_UNITS overrides the
-// default (a tuning aid; 0 switches the warm-up off).
+// Units per CTA whose tiles are prefetched into L2 ahead of the dependency wait (0 switches the warm-up off).
+// Measured optimum on B200 for the 64-stream ragged batch: 4 (8 and more compete with the launch still running).
+// A build with -DQM_DECODE_TUNING reads QM_DECODE_PREFETCH_UNITS from the environment instead.
 int decode_prefetch_units() {
+#ifdef QM_DECODE_TUNING
     static const int value = [] {
         const char* text = getenv("QM_DECODE_PREFETCH_UNITS");
         int v = text ? atoi(text) : 4;
         return v < 0 ? 0 : (v > 32 ? 32 : v);
     }();
     return value;
+#else
+    return 4;
+#endif
 }
 
 int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const int32_t* seq_lens,
@@ -936,13 +967,12 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
     if (grid > kMaxGrid) grid = kMaxGrid;
 
     const int chunk_cap = kMaxBatchPerLaunch;
-    const int segs_cap = (batch < chunk_cap ? batch : chunk_cap) * pool->kv_heads;
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     DecodeArgs a{};
     a.key_pool = qm_kv_pool_key_ptr(pool, layer);
     a.value_pool = qm_kv_pool_value_ptr(pool, layer);
-    a.ws_partials = reinterpret_cast<float*>(ws);
-    a.ws_count = reinterpret_cast<int32_t*>(ws + partials_bytes(segs_cap));
+    a.ws_count = reinterpret_cast<int32_t*>(ws);
+    a.ws_partials = reinterpret_cast<float*>(ws + kCounterRegionBytes);
     a.status = pool->status_dev;
     a.kv_heads = pool->kv_heads;
     a.max_pages = max_pages;
@@ -1002,7 +1032,7 @@ extern "C" {
 int64_t qm_decode_workspace_bytes(int32_t batch, int32_t kv_heads) {
     if (batch < 0 || kv_heads < 1) return 0;
     const int segs = (batch < kMaxBatchPerLaunch ? batch : kMaxBatchPerLaunch) * kv_heads;
-    return (int64_t)partials_bytes(segs) + (int64_t)segs * 2 * sizeof(int32_t) + 256;
+    return (int64_t)kCounterRegionBytes + (int64_t)partials_bytes(segs) + 256;
 }
 
 int32_t qm_decode_workspace_init(void* workspace, int64_t workspace_bytes, void* stream) {
@@ -1072,8 +1102,8 @@ int32_t qm_attention_combine(const float* partials, int32_t parts, int32_t rows,
 constexpr int kStaticMaxBatch = 64;
 constexpr int kStaticMaxKvHeads = 8;
 constexpr size_t kStaticScratchBytes =
-    (size_t)(kMaxGrid + kStaticMaxBatch * kStaticMaxKvHeads) * 2 * kPartialStride * sizeof(float)   // partials
-    + (size_t)kStaticMaxBatch * kStaticMaxKvHeads * 2 * sizeof(int32_t)                             // arrival counters
+    kCounterRegionBytes                                                                             // arrival counters
+    + (size_t)(kMaxGrid + kStaticMaxBatch * kStaticMaxKvHeads) * 2 * kPartialStride * sizeof(float)  // partials
     + 256;
 
 static __device__ __align__(256) unsigned char qm_static_decode_scratch[kStaticScratchBytes];
@@ -1082,20 +1112,22 @@ namespace {
 
 constexpr int kMaxDevices = 64;
 
-// Device address of the scratch array on `device`.  In host code the array's
-// name is only a handle for the runtime, not something a kernel can be given,
-// so the address is looked up once per device (with that device current) and
-// remembered.
+// Device address of the scratch array on `device`, which must be the current
+// device.  In host code the array's name is only a handle for the runtime, not
+// something a kernel can be given, so the address is looked up once per device
+// and remembered.
 int32_t static_scratch_address(int device, void** address_out) {
     static std::mutex guard;
     static void* known[kMaxDevices] = {};
     if (device < 0 || device >= kMaxDevices) return qm_fail(QM_EINVAL, "device index out of range for the static scratch");
+    // Every call, not only the first: the launch goes to the current device, and the pool's pointers and the
+    // address remembered here belong to the pool's device.
+    int current = -1;
+    QM_CUDA_TRY(cudaGetDevice(&current), "get current device");
+    if (current != device)
+        return qm_fail(QM_EINVAL, "the pool's device must be the current device for the static-scratch entry points");
     std::lock_guard<std::mutex> lock(guard);
     if (!known[device]) {
-        int current = -1;
-        QM_CUDA_TRY(cudaGetDevice(&current), "get current device");
-        if (current != device)
-            return qm_fail(QM_EINVAL, "the pool's device must be current on the first qm_decode_attention_static call");
         void* address = nullptr;
         QM_CUDA_TRY(cudaGetSymbolAddress(&address, qm_static_decode_scratch), "look up static decode scratch");
         if (!address) return qm_fail(QM_ECUDA, "static decode scratch has no device address");
@@ -1124,6 +1156,19 @@ extern "C" int32_t qm_decode_attention_static(qm_kv_pool* pool, int32_t layer, c
     // kernel puts every counter it used back to zero before it finishes, so no
     // clearing is needed here; partial slots are always written before they are
     // read within one call, so leftovers from the previous call are never used.
+    // The one exception is a call that reported QM_DEVSTAT_TIMEOUT: it may leave
+    // counters behind, and qm_decode_static_scratch_reset puts them back.
     return run_decode(pool, layer, q_rot, seq_lens, page_table, max_pages, batch, q_heads, out, nullptr, scratch,
                       (int64_t)kStaticScratchBytes, static_cast<cudaStream_t>(stream), 0);
+}
+
+extern "C" int32_t qm_decode_static_scratch_reset(qm_kv_pool* pool, void* stream) {
+    if (!pool) return qm_fail(QM_EINVAL, "pool is null");
+    void* scratch = nullptr;
+    const int32_t looked_up = static_scratch_address(pool->device, &scratch);
+    if (looked_up != QM_OK) return looked_up;
+    // a memset on an address that already exists: nothing is allocated
+    QM_CUDA_TRY(cudaMemsetAsync(scratch, 0, kCounterRegionBytes, static_cast<cudaStream_t>(stream)),
+                "clear static decode scratch counters");
+    return QM_OK;
 }

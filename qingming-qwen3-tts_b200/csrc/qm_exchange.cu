@@ -2,15 +2,25 @@
 //
 // Used when a very long stream's keys are split over several GPUs: every rank has the partial softmax state
 // (m, l, o[128]) of each (stream, query head) row over its own slice.  Instead of a library all-gather followed by
-// a combine kernel, each rank's kernel
-//   1. stores its rows straight into the exchange buffer of every peer (plain peer-to-peer stores over NVLink),
-//   2. publishes them with a system-scope release on a per-source counter in the peer's buffer,
-//   3. waits (bounded) until the counters of all sources in its OWN buffer have reached this call's value,
-//   4. folds the world's partials of each row in rank order and writes the bf16 context.
-// Every rank runs the same kernel at the same time on its own GPU.  Counters only grow (call number * rows), the
-// payload is double-buffered by call parity, so nothing has to be cleared between calls.  No multicast, no TMA:
+// a combine kernel, each rank's kernel, one CTA per row,
+//   1. takes the row's next sequence number from a counter in its OWN buffer (device state, so the host passes no
+//      call number and a captured launch can be replayed),
+//   2. stores its row straight into slot (sequence parity, this rank, row) of every rank's buffer - plain
+//      peer-to-peer stores over NVLink - and then publishes it by storing the sequence number into the slot's
+//      arrival word with a system-scope release,
+//   3. waits (bounded) until the arrival words of ALL ranks for this row in its own buffer carry that number,
+//   4. folds the world's partials of the row in rank order and writes the bf16 context.
+// A row's CTA waits only for that same row of the other ranks, so rows do not depend on one another.  Slots are
+// double-buffered by sequence parity: a peer can be at most one call ahead (it cannot finish call n + 1 without
+// this rank's row of call n + 1), so it never overwrites a slot that is still being read.  No multicast, no TMA:
 // ordinary global stores and loads on peer addresses.  The reference has no multi-GPU path; this is new.
+//
+// Also here: the exchange object that owns such a buffer and maps the peers' buffers through CUDA IPC handles (for
+// hosts with one process per GPU) or takes peer pointers directly (one process driving several GPUs).
 #include <math_constants.h>
+
+#include <cstring>
+#include <new>
 
 #include "qm_common.cuh"
 
@@ -19,22 +29,31 @@ namespace {
 constexpr int kPartialWidth = kHeadDim + 2;        // m, l, o[128]
 constexpr int kExchangeThreads = 160;              // 130 payload lanes, rounded up to warps
 constexpr uint32_t kExchangeSpinLimit = 1u << 20;
+constexpr int kMaxWorld = 32;
 
 struct ExchangeArgs {
     const float* local;              // [rows][130] this rank's partials (m in natural-log domain)
     unsigned char* const* peers;     // [world] device pointers to every rank's exchange buffer (own included)
     uint16_t* out;                   // [rows][128]
     uint32_t* status;
-    unsigned long long epoch;        // 1, 2, 3, ... : number of this call
     int world, rank, rows, rows_capacity;
 };
 
-// buffer layout: float payload[2][world][rows_capacity][130]; then unsigned long long arrived[world]
+// buffer layout:  float    payload[2][world][rows_capacity][130]
+//                 uint32_t arrived[2][world][rows_capacity]     sequence number of the payload in that slot
+//                 uint32_t calls[rows_capacity]                 how often this rank has exchanged that row
+__host__ __device__ __forceinline__ size_t payload_bytes(int world, int rows_capacity) {
+    return (size_t)2 * world * rows_capacity * kPartialWidth * sizeof(float);
+}
 __device__ __forceinline__ size_t payload_offset(const ExchangeArgs& a, int slot, int source, int row) {
     return ((((size_t)slot * a.world + source) * a.rows_capacity + row) * kPartialWidth) * sizeof(float);
 }
-__device__ __forceinline__ size_t counter_offset(const ExchangeArgs& a, int source) {
-    return (size_t)2 * a.world * a.rows_capacity * kPartialWidth * sizeof(float) + (size_t)source * sizeof(unsigned long long);
+__device__ __forceinline__ size_t arrived_offset(const ExchangeArgs& a, int slot, int source, int row) {
+    return payload_bytes(a.world, a.rows_capacity) + (((size_t)slot * a.world + source) * a.rows_capacity + row) * sizeof(uint32_t);
+}
+__device__ __forceinline__ size_t calls_offset(const ExchangeArgs& a, int row) {
+    return payload_bytes(a.world, a.rows_capacity) + (size_t)2 * a.world * a.rows_capacity * sizeof(uint32_t) +
+           (size_t)row * sizeof(uint32_t);
 }
 
 __global__ void __launch_bounds__(kExchangeThreads) qm_exchange_combine_kernel(const ExchangeArgs a) {
@@ -42,11 +61,20 @@ __global__ void __launch_bounds__(kExchangeThreads) qm_exchange_combine_kernel(c
     pdl_wait();
     const int row = blockIdx.x;
     const int t = threadIdx.x;
-    const int slot = (int)(a.epoch & 1ull);
+    __shared__ uint32_t sequence_shared;
     __shared__ int timed_out;
-    if (t == 0) timed_out = 0;
+    if (t == 0) {
+        uint32_t* calls = reinterpret_cast<uint32_t*>(a.peers[a.rank] + calls_offset(a, row));
+        const uint32_t sequence = *calls + 1u;      // only this row's CTA of this rank ever touches the word
+        *calls = sequence;
+        sequence_shared = sequence;
+        timed_out = 0;
+    }
+    __syncthreads();
+    const uint32_t sequence = sequence_shared;
+    const int slot = (int)(sequence & 1u);
 
-    // 1. my row to every rank's buffer
+    // my row into every rank's buffer, then its arrival word
     if (t < kPartialWidth) {
         const float v = a.local[(size_t)row * kPartialWidth + t];
         for (int p = 0; p < a.world; ++p)
@@ -54,21 +82,18 @@ __global__ void __launch_bounds__(kExchangeThreads) qm_exchange_combine_kernel(c
     }
     __threadfence_system();
     __syncthreads();
-    // 2. one arrival per row on every rank's counter for this source
     if (t < a.world) {
-        unsigned long long* counter = reinterpret_cast<unsigned long long*>(a.peers[t] + counter_offset(a, a.rank));
-        asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(counter), "l"(1ull) : "memory");
+        uint32_t* word = reinterpret_cast<uint32_t*>(a.peers[t] + arrived_offset(a, slot, a.rank, row));
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(word), "r"(sequence) : "memory");
     }
-    // 3. wait for every source's rows of this call
+    // every source's row of this call
     if (t < a.world) {
-        const unsigned long long* counter =
-            reinterpret_cast<const unsigned long long*>(a.peers[a.rank] + counter_offset(a, t));
-        const unsigned long long want = a.epoch * (unsigned long long)a.rows;
+        const uint32_t* word = reinterpret_cast<const uint32_t*>(a.peers[a.rank] + arrived_offset(a, slot, t, row));
         bool ok = false;
         for (uint32_t spin = 0; spin < kExchangeSpinLimit; ++spin) {
-            unsigned long long seen;
-            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(counter) : "memory");
-            if (seen >= want) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(word) : "memory");
+            if ((int32_t)(seen - sequence) >= 0) {
                 ok = true;
                 break;
             }
@@ -80,7 +105,7 @@ __global__ void __launch_bounds__(kExchangeThreads) qm_exchange_combine_kernel(c
         }
     }
     __syncthreads();
-    // 4. fold in rank order
+    // fold in rank order
     if (t < kHeadDim) {
         const unsigned char* mine = a.peers[a.rank];
         float big = -CUDART_INF_F;
@@ -99,28 +124,59 @@ __global__ void __launch_bounds__(kExchangeThreads) qm_exchange_combine_kernel(c
     }
 }
 
+// Rows one launch may carry: every row's CTA must be able to be resident at once.  A CTA spins until the same row
+// of every other rank has arrived; if the ranks' hardware handed out CTAs in different orders and only some fit,
+// two ranks could each hold rows the other has not started.  With all CTAs resident that cannot happen.
+int32_t exchange_row_limit(qm_kv_pool* pool, int* limit_out) {
+    static thread_local int known_device = -1, known_limit = 0;
+    if (known_device != pool->device) {
+        int per_sm = 0;
+        QM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qm_exchange_combine_kernel, kExchangeThreads, 0),
+                    "query exchange kernel occupancy");
+        known_limit = per_sm * pool->sm_count;
+        known_device = pool->device;
+    }
+    *limit_out = known_limit;
+    return QM_OK;
+}
+
 }  // namespace
+
+struct qm_exchange {
+    int device;
+    int world, rank, rows_capacity;
+    size_t bytes;
+    unsigned char* own;                 // this rank's buffer (cudaMalloc)
+    unsigned char* mapped[kMaxWorld];   // every rank's buffer as seen from this process; [rank] == own
+    bool opened_by_ipc[kMaxWorld];
+    unsigned char** table_dev;          // device copy of mapped[0..world)
+    bool peers_known;
+};
 
 extern "C" {
 
 int64_t qm_exchange_buffer_bytes(int32_t world, int32_t rows_capacity) {
     if (world < 1 || rows_capacity < 1) return 0;
-    return (int64_t)2 * world * rows_capacity * kPartialWidth * (int64_t)sizeof(float) + (int64_t)world * 8 + 64;
+    return (int64_t)payload_bytes(world, rows_capacity) + (int64_t)2 * world * rows_capacity * 4 + (int64_t)rows_capacity * 4 + 64;
 }
 
 int32_t qm_attention_exchange_combine(qm_kv_pool* pool, const float* local_partials, void* const* peer_buffers_dev,
-                                      int32_t world, int32_t rank, int32_t rows, int32_t rows_capacity, uint64_t epoch,
-                                      uint16_t* out, void* stream) {
+                                      int32_t world, int32_t rank, int32_t rows, int32_t rows_capacity, uint16_t* out,
+                                      void* stream) {
     if (!pool || !local_partials || !peer_buffers_dev || !out) return qm_fail(QM_EINVAL, "null pointer");
-    if (world < 1 || world > 32 || rank < 0 || rank >= world || rows < 0 || rows > rows_capacity || epoch == 0)
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || rows < 0 || rows > rows_capacity)
         return qm_fail(QM_EINVAL, "invalid exchange geometry");
     if (rows == 0) return QM_OK;
+    int limit = 0;
+    const int32_t rc = exchange_row_limit(pool, &limit);
+    if (rc != QM_OK) return rc;
+    if (rows > limit)
+        return qm_fail(QM_ECAPACITY, "more rows than can be resident on the GPU at once; exchange them in several calls");
     ExchangeArgs a{};
     a.local = local_partials;
     a.peers = reinterpret_cast<unsigned char* const*>(peer_buffers_dev);
     a.out = out;
     a.status = pool->status_dev;
-    a.epoch = epoch;
     a.world = world;
     a.rank = rank;
     a.rows = rows;
@@ -128,6 +184,108 @@ int32_t qm_attention_exchange_combine(qm_kv_pool* pool, const float* local_parti
     QM_CUDA_TRY(qm_launch(qm_exchange_combine_kernel, dim3(rows), dim3(kExchangeThreads), 0, static_cast<cudaStream_t>(stream), a),
                 "partial exchange + combine launch");
     return QM_OK;
+}
+
+// ---- the exchange object: owns this rank's buffer, maps the peers'
+
+int32_t qm_exchange_create(int32_t world, int32_t rank, int32_t rows_capacity, qm_exchange** exchange_out) {
+    if (!exchange_out) return qm_fail(QM_EINVAL, "exchange_out is null");
+    *exchange_out = nullptr;
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || rows_capacity < 1)
+        return qm_fail(QM_EINVAL, "invalid exchange geometry");
+    qm_exchange* ex = new (std::nothrow) qm_exchange();
+    if (!ex) return qm_fail(QM_ENOMEM, "host allocation of exchange object failed");
+    std::memset(ex, 0, sizeof(*ex));
+    ex->world = world;
+    ex->rank = rank;
+    ex->rows_capacity = rows_capacity;
+    ex->bytes = (size_t)qm_exchange_buffer_bytes(world, rows_capacity);
+    cudaError_t status = cudaGetDevice(&ex->device);
+    if (status == cudaSuccess) status = cudaMalloc(&ex->own, ex->bytes);
+    if (status == cudaSuccess) status = cudaMalloc(&ex->table_dev, sizeof(unsigned char*) * kMaxWorld);
+    if (status == cudaSuccess) status = cudaMemset(ex->own, 0, ex->bytes);
+    if (status == cudaSuccess) status = cudaDeviceSynchronize();
+    if (status != cudaSuccess) {
+        const int32_t code = qm_fail_cuda(status, "allocate exchange buffer");
+        qm_exchange_destroy(ex);
+        return code;
+    }
+    ex->mapped[rank] = ex->own;
+    *exchange_out = ex;
+    return QM_OK;
+}
+
+int32_t qm_exchange_destroy(qm_exchange* ex) {
+    if (!ex) return QM_OK;
+    for (int r = 0; r < ex->world; ++r)
+        if (ex->opened_by_ipc[r] && ex->mapped[r]) cudaIpcCloseMemHandle(ex->mapped[r]);
+    if (ex->table_dev) cudaFree(ex->table_dev);
+    if (ex->own) cudaFree(ex->own);
+    delete ex;
+    return QM_OK;
+}
+
+void* qm_exchange_local_buffer(qm_exchange* ex) { return ex ? ex->own : nullptr; }
+
+int32_t qm_exchange_ipc_handle(qm_exchange* ex, void* handle_out) {
+    if (!ex || !handle_out) return qm_fail(QM_EINVAL, "null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == QM_IPC_HANDLE_BYTES, "IPC handle size");
+    cudaIpcMemHandle_t handle;
+    QM_CUDA_TRY(cudaIpcGetMemHandle(&handle, ex->own), "export exchange buffer");
+    std::memcpy(handle_out, &handle, sizeof(handle));
+    return QM_OK;
+}
+
+static int32_t upload_peer_table(qm_exchange* ex) {
+    QM_CUDA_TRY(cudaMemcpy(ex->table_dev, ex->mapped, sizeof(unsigned char*) * ex->world, cudaMemcpyHostToDevice),
+                "upload peer pointer table");
+    ex->peers_known = true;
+    return QM_OK;
+}
+
+int32_t qm_exchange_open_peers(qm_exchange* ex, const void* handles) {
+    if (!ex || !handles) return qm_fail(QM_EINVAL, "null pointer");
+    const unsigned char* bytes = static_cast<const unsigned char*>(handles);
+    for (int r = 0; r < ex->world; ++r) {
+        if (r == ex->rank || ex->mapped[r]) continue;
+        cudaIpcMemHandle_t handle;
+        std::memcpy(&handle, bytes + (size_t)r * QM_IPC_HANDLE_BYTES, sizeof(handle));
+        void* mapped = nullptr;
+        QM_CUDA_TRY(cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess), "map a peer's exchange buffer");
+        ex->mapped[r] = static_cast<unsigned char*>(mapped);
+        ex->opened_by_ipc[r] = true;
+    }
+    return upload_peer_table(ex);
+}
+
+int32_t qm_exchange_set_peers(qm_exchange* ex, void* const* peer_buffers) {
+    if (!ex || !peer_buffers) return qm_fail(QM_EINVAL, "null pointer");
+    for (int r = 0; r < ex->world; ++r) {
+        if (r == ex->rank) continue;
+        if (!peer_buffers[r]) return qm_fail(QM_EINVAL, "a peer buffer pointer is null");
+        ex->mapped[r] = static_cast<unsigned char*>(peer_buffers[r]);
+        ex->opened_by_ipc[r] = false;
+    }
+    return upload_peer_table(ex);
+}
+
+int32_t qm_exchange_reset(qm_exchange* ex, void* stream) {
+    if (!ex) return qm_fail(QM_EINVAL, "exchange is null");
+    QM_CUDA_TRY(cudaMemsetAsync(ex->own, 0, ex->bytes, static_cast<cudaStream_t>(stream)), "clear exchange buffer");
+    return QM_OK;
+}
+
+int32_t qm_exchange_combine(qm_kv_pool* pool, qm_exchange* ex, const float* local_partials, int32_t rows, uint16_t* out,
+                            void* stream) {
+    if (!ex) return qm_fail(QM_EINVAL, "exchange is null");
+    if (!ex->peers_known && ex->world > 1)
+        return qm_fail(QM_EINVAL, "peer buffers are not mapped yet: call qm_exchange_open_peers or qm_exchange_set_peers first");
+    if (!ex->peers_known) {
+        const int32_t rc = upload_peer_table(ex);
+        if (rc != QM_OK) return rc;
+    }
+    return qm_attention_exchange_combine(pool, local_partials, reinterpret_cast<void* const*>(ex->table_dev), ex->world, ex->rank,
+                                         rows, ex->rows_capacity, out, stream);
 }
 
 }  // extern "C"

@@ -73,34 +73,6 @@ struct PrefillArgs {
     int max_qblocks;
 };
 
-// 2^x for a pair on the FMA pipe instead of the special-function unit (which, at 16 results per clock per SM,
-// would otherwise bound the softmax): round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a degree-3
-// minimax polynomial for 2^f on [-0.5, 0.5] (max relative error 7.5e-5, far below a bf16 ulp), then n is added
-// into the exponent field.  x is clamped at -125 so that the biased exponent stays positive (2^-125 is 0 in bf16).
-__device__ __forceinline__ float2 exp2_poly_pair(float2 x) {
-    const float2 magic = make_float2(12582912.0f, 12582912.0f);
-    const float2 neg_magic = make_float2(-12582912.0f, -12582912.0f);
-    const float2 minus_one = make_float2(-1.0f, -1.0f);
-    x.x = fmaxf(x.x, -125.0f);
-    x.y = fmaxf(x.y, -125.0f);
-    const float2 t = fadd2(x, magic);
-    const float2 n = fadd2(t, neg_magic);
-    const float2 f = ffma2(n, minus_one, x);
-    float2 p = ffma2(f, make_float2(0.0551716685f, 0.0551716685f), make_float2(0.2426111251f, 0.2426111251f));
-    p = ffma2(p, f, make_float2(0.6932609677f, 0.6932609677f));
-    p = ffma2(p, f, make_float2(0.9999280572f, 0.9999280572f));
-    float2 r;
-    r.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23));
-    r.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23));
-    return r;
-}
-
-// Of every 8 column pairs, this many take the polynomial path; the rest use ex2.approx.
-#ifndef QM_POLY_PAIRS_OF_8
-#define QM_POLY_PAIRS_OF_8 0
-#endif
-constexpr int kPolyPairsOf8 = QM_POLY_PAIRS_OF_8;
-
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 qm_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                             const __grid_constant__ CUtensorMap v_map, const PrefillArgs a) {
@@ -340,7 +312,7 @@ qm_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 for (int i = 0; i < 16; ++i) {
                     const float2 x = ffma2(make_float2(__uint_as_float(sreg[cch][2 * i]), __uint_as_float(sreg[cch][2 * i + 1])),
                                            c2, negm2);
-                    const float2 p = (i & 7) < kPolyPairsOf8 ? exp2_poly_pair(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                    const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
                     sum2[i & 3] = fadd2(sum2[i & 3], p);
                     preg[i] = pack_bf16x2(p.x, p.y);
                 }

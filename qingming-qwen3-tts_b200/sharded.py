@@ -68,14 +68,12 @@ class PeerExchange:
     """Exchange + combine of the partials in one kernel over peer memory (qm_attention_exchange_combine) instead of
     an all-gather plus a combine kernel.  The exchange buffers are symmetric memory: every rank allocates one and
     maps the others' (torch.distributed._symmetric_memory over CUDA IPC / NVLink).  Call `run` at the same point on
-    every rank."""
+    every rank, with the same number of rows."""
 
     def __init__(self, engine, rows_capacity: int, group=None):
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
-
-        from . import _check, _ptr, _stream  # noqa: F401
 
         self.engine = engine
         self.group = group if group is not None else dist.group.WORLD
@@ -87,7 +85,6 @@ class PeerExchange:
         self.buffer.zero_()
         self.handle = symm_mem.rendezvous(self.buffer, self.group.group_name)
         self.peer_ptrs = torch.tensor([int(p) for p in self.handle.buffer_ptrs], dtype=torch.int64, device="cuda")
-        self.epoch = 0
         torch.cuda.synchronize()
         dist.barrier(self.group)          # every buffer is zeroed and mapped before the first kernel touches it
 
@@ -100,14 +97,114 @@ class PeerExchange:
         rows = partial.shape[0] * partial.shape[1]
         if out is None:
             out = torch.empty((partial.shape[0], partial.shape[1], HEAD_DIM), dtype=torch.bfloat16, device="cuda")
-        self.epoch += 1
         _check(self.engine.lib.qm_attention_exchange_combine(
             self.engine.pool, _ptr(partial), _ptr(self.peer_ptrs), self.world, self.rank, rows, self.rows_capacity,
-            self.epoch, _ptr(out), _stream()))
+            _ptr(out), _stream()))
         return out
 
 
-def sharded_decode_attention_peer(engine, exchange: PeerExchange, layer, q_rot, local_seq_lens, page_table, out=None):
+class IpcExchange:
+    """The same exchange on buffers the library allocates itself and shares through CUDA IPC handles
+    (qm_exchange_create / qm_exchange_ipc_handle / qm_exchange_open_peers): what a C++ host with one process per GPU
+    uses.  Here the 64-byte handles travel through torch.distributed's object all-gather."""
+
+    def __init__(self, engine, rows_capacity: int, group=None):
+        import ctypes
+
+        import torch
+        import torch.distributed as dist
+
+        from . import IPC_HANDLE_BYTES, _check
+
+        self.engine = engine
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        handle = ctypes.c_void_p()
+        _check(engine.lib.qm_exchange_create(self.world, self.rank, rows_capacity, ctypes.byref(handle)))
+        self.handle = handle
+        mine = ctypes.create_string_buffer(IPC_HANDLE_BYTES)
+        _check(engine.lib.qm_exchange_ipc_handle(self.handle, mine))
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, bytes(mine.raw), group=self.group)
+        packed = ctypes.create_string_buffer(b"".join(everyone), IPC_HANDLE_BYTES * self.world)
+        _check(engine.lib.qm_exchange_open_peers(self.handle, packed))
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+
+    def run(self, partial, out=None):
+        import torch
+
+        from . import HEAD_DIM, _check, _ptr, _stream
+
+        rows = partial.shape[0] * partial.shape[1]
+        if out is None:
+            out = torch.empty((partial.shape[0], partial.shape[1], HEAD_DIM), dtype=torch.bfloat16, device="cuda")
+        _check(self.engine.lib.qm_exchange_combine(self.engine.pool, self.handle, _ptr(partial), rows, _ptr(out), _stream()))
+        return out
+
+    def close(self):
+        if self.handle:
+            self.engine.lib.qm_exchange_destroy(self.handle)
+            self.handle = None
+
+
+def sharded_decode_attention_peer(engine, exchange, layer, q_rot, local_seq_lens, page_table, out=None):
     """Split-KV kernel over this rank's slice, then the one-kernel peer-memory exchange + combine."""
     partial = engine.launch_attention_partial(layer, q_rot, local_seq_lens, page_table)
     return exchange.run(partial, out=out)
+
+
+class NcclSharded:
+    """qm_decode_attention_sharded on a communicator the library's own helpers create (ncclGetUniqueId on rank 0,
+    passed to the others through torch.distributed, ncclCommInitRank on every rank): the path a C++ host takes,
+    driven from Python for the tests and the benchmark."""
+
+    def __init__(self, engine, batch: int, group=None):
+        import ctypes
+
+        import torch
+        import torch.distributed as dist
+
+        from . import PARTIAL_STRIDE, _check
+
+        self.engine = engine
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        ident = ctypes.create_string_buffer(128)
+        if self.rank == 0:
+            _check(engine.lib.qm_nccl_unique_id(ident))
+        box = [bytes(ident.raw)]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, 0), group=self.group)
+        ident = ctypes.create_string_buffer(box[0], 128)
+        comm = ctypes.c_void_p()
+        _check(engine.lib.qm_nccl_comm_init_rank(ctypes.byref(comm), self.world, ident, self.rank))
+        self.comm = comm
+        self.send = torch.empty((batch, engine.q_heads, PARTIAL_STRIDE), dtype=torch.float32, device="cuda")
+        self.recv = torch.empty((self.world, batch, engine.q_heads, PARTIAL_STRIDE), dtype=torch.float32, device="cuda")
+
+    def run(self, layer, q_rot, local_seq_lens, page_table, out=None):
+        import torch
+
+        from . import _check, _ptr, _stream
+
+        batch = q_rot.shape[0]
+        if out is None:
+            out = torch.empty_like(q_rot)
+        ws = self.engine.workspace(batch)
+        _check(self.engine.lib.qm_decode_attention_sharded(
+            self.engine.pool, layer, _ptr(q_rot), _ptr(local_seq_lens), _ptr(page_table), page_table.shape[1], batch,
+            self.engine.q_heads, _ptr(out), _ptr(self.send), _ptr(self.recv), self.world, _ptr(ws), ws.numel(),
+            self.comm, _stream()))
+        return out
+
+    def wait(self, deadline_ms=10000):
+        from . import _check, _stream
+
+        _check(self.engine.lib.qm_nccl_wait(self.comm, _stream(), deadline_ms))
+
+    def close(self):
+        if self.comm:
+            self.engine.lib.qm_nccl_comm_destroy(self.comm)
+            self.comm = None

@@ -54,16 +54,63 @@ def main():
     sums = [torch.zeros_like(mine) for _ in range(world)]
     dist.all_gather(sums, mine)
     assert all(int(x) == int(sums[0]) for x in sums)
-    # the same step through the one-kernel peer-memory exchange: identical bits, three calls in a row
-    exchange = sh.PeerExchange(eng, rows_capacity=sc.batch * 16)
+    # ---- the same step through the other exchange paths.  Every call gets different inputs (the streams' queries
+    # rotated, all four streams having the same length) and every call is checked, so an exchange that did not
+    # wait for its peers, or folded a stale slot, cannot pass.
     lens_dev = torch.from_numpy(local_lens.astype(np.int32)).cuda()
-    for _ in range(3):
-        out_peer = sh.sharded_decode_attention_peer(eng, exchange, 0, q_rot, lens_dev, table)
+    variants = [torch.roll(q_rot, shifts=i, dims=0).contiguous() for i in range(4)]
+    wanted = []
+    for qv in variants:
+        wanted.append(scenario._bits(sh.sharded_decode_attention(eng, runner, 0, qv, lens_dev, table)).copy())
+    assert np.array_equal(wanted[0], bits)
+    assert not np.array_equal(wanted[1], wanted[0])
+
+    def check(name, call):
+        for i, qv in enumerate(variants):
+            got = scenario._bits(call(qv, lens_dev, table))
+            assert np.array_equal(got, wanted[i]), f"{name}: call {i} differs from all-gather + combine"
+        # fewer rows in one call, then all rows again: the per-row call counters keep the ranks in step
+        got = scenario._bits(call(variants[2][:2].contiguous(), lens_dev[:2].contiguous(), table[:2].contiguous()))
+        assert np.array_equal(got, wanted[2][:2]), f"{name}: two-stream call differs"
+        got = scenario._bits(call(variants[3], lens_dev, table))
+        assert np.array_equal(got, wanted[3]), f"{name}: call after a smaller one differs"
+
+    # 1. one kernel over torch symmetric memory
+    exchange = sh.PeerExchange(eng, rows_capacity=sc.batch * 16)
+    check("peer exchange", lambda qv, ln, tb_: sh.sharded_decode_attention_peer(eng, exchange, 0, qv, ln, tb_))
+    # ... and replayed from a CUDA graph with new inputs each time (the call number is device state)
+    static_q = variants[0].clone()
+    out_graph = torch.empty_like(static_q)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        sh.sharded_decode_attention_peer(eng, exchange, 0, static_q, lens_dev, table, out=out_graph)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        sh.sharded_decode_attention_peer(eng, exchange, 0, static_q, lens_dev, table, out=out_graph)
+    for i in (1, 2, 3, 0, 2):
+        static_q.copy_(variants[i])
+        graph.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(scenario._bits(out_graph), wanted[i]), f"graph replay with inputs {i} differs"
+    # 2. the same kernel on buffers shared through CUDA IPC handles (the C++ host's route)
+    ipc = sh.IpcExchange(eng, rows_capacity=sc.batch * 16)
+    check("ipc exchange", lambda qv, ln, tb_: sh.sharded_decode_attention_peer(eng, ipc, 0, qv, ln, tb_))
+    # 3. the C entry point that does partial -> ncclAllGather -> combine on a communicator of its own
+    nccl = sh.NcclSharded(eng, sc.batch)
+    for i, qv in enumerate(variants):
+        got = scenario._bits(nccl.run(0, qv, lens_dev, table))
+        nccl.wait(deadline_ms=20000)
+        assert np.array_equal(got, wanted[i]), f"qm_decode_attention_sharded: call {i} differs"
     torch.cuda.synchronize()
     assert eng.status() == 0
-    assert np.array_equal(scenario._bits(out_peer), bits), "peer-memory exchange differs from all-gather + combine"
     dist.barrier()
-    del exchange
+    nccl.close()
+    ipc.close()
+    del exchange, graph
     eng.close()
     dist.barrier()
     if rank == 0:
