@@ -384,3 +384,57 @@ def ref_final_head(logits, history=None, generation_index=0, flags=0, top_k=0, t
                                 ctypes.byref(code))
     assert rc == 0, rc
     return int(code.value), processed, int(state.value), hist
+
+
+# -------------------------------- the reference's code-predictor kernels (GPU, optional; fixed predictor shapes)
+
+def ref_predictor_qkv_m1(x, q_w, k_w, v_w):
+    q = np.empty(q_w.shape[0], dtype=np.uint16)
+    k = np.empty(k_w.shape[0], dtype=np.uint16)
+    v = np.empty(v_w.shape[0], dtype=np.uint16)
+    rc = ref().qmref_predictor_qkv_m1(_p(_u16(x)), _p(_u16(q_w)), _p(_u16(k_w)), _p(_u16(v_w)), _p(q), _p(k), _p(v))
+    assert rc == 0, rc
+    return q, k, v
+
+
+def ref_predictor_qk_norm_rope_cache_m1(q, k, v, q_w, k_w, cos_row, sin_row, key_cache, value_cache, position):
+    """Caches [8][16][128] are updated in place; returns q_rot [16][128]."""
+    q = _u16(q)
+    q_rot = np.empty_like(q)
+    rc = ref().qmref_predictor_qk_norm_rope_cache_m1(_p(q), _p(_u16(k)), _p(_u16(v)), _p(_u16(q_w)), _p(_u16(k_w)),
+                                                     _p(_u16(cos_row)), _p(_u16(sin_row)), _p(q_rot), _p(key_cache),
+                                                     _p(value_cache), c_int(position))
+    assert rc == 0, rc
+    return q_rot
+
+
+def ref_predictor_attention_m1(q_rot, key_cache, value_cache, key_length):
+    q_rot = _u16(q_rot)
+    out = np.empty_like(q_rot)
+    rc = ref().qmref_predictor_attention_m1(_p(q_rot), _p(_u16(key_cache)), _p(_u16(value_cache)), _p(out), c_int(key_length))
+    assert rc == 0, rc
+    return out
+
+
+def ref_predictor_linear_m1(x, w, residual=None):
+    x, w = _u16(x), _u16(w)
+    out = np.empty(w.shape[0], dtype=np.uint16)
+    rc = ref().qmref_predictor_linear_m1(_p(x), _p(w), _p(_u16(residual)) if residual is not None else None, _p(out),
+                                         c_int(w.shape[0]), c_int(w.shape[1]))
+    assert rc == 0, rc
+    return out
+
+
+def ref_predictor_add_postnorm_m1(hidden, attention, w):
+    hidden = _u16(hidden)
+    residual, normalized = np.empty_like(hidden), np.empty_like(hidden)
+    rc = ref().qmref_predictor_add_postnorm_m1(_p(hidden), _p(_u16(attention)), _p(_u16(w)), _p(residual), _p(normalized))
+    assert rc == 0, rc
+    return residual, normalized
+
+
+def ref_predictor_gate_up_swiglu_m1(x, gate_w, up_w):
+    out = np.empty(gate_w.shape[0], dtype=np.uint16)
+    rc = ref().qmref_predictor_gate_up_swiglu_m1(_p(_u16(x)), _p(_u16(gate_w)), _p(_u16(up_w)), _p(out))
+    assert rc == 0, rc
+    return out

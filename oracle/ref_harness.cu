@@ -23,6 +23,13 @@
 //   talker_linear_fused_kernel                :15250   launcher :17646
 //   talker_add_postnorm_fused_kernel          :16258   launcher :17989
 //   talker_gate_up_swiglu_fused_kernel        :16348   launcher :18020
+// and the code predictor's one-row kernels (namespace code_predictor; launchers :13395-13575):
+//   predictor_qkv_m1_fused_kernel             :12063   launcher qkv_m1
+//   predictor_qk_norm_rope_cache_m1_kernel    :12150   launcher qk_norm_rope_cache_m1
+//   predictor_attention_gqa2_m1_kernel        :12331   launcher attention_m1
+//   predictor_linear_m1_fused_kernel          :12596   launcher linear_m1
+//   predictor_add_postnorm_m1_kernel          :12675   launcher add_postnorm_m1
+//   predictor_gate_up_swiglu_m1_kernel        :12753   launcher gate_up_swiglu_m1
 // Launch shapes and shared-memory sizes follow the cited launchers.
 
 #define main qm_refharness_unused_reference_main
@@ -375,6 +382,130 @@ int qmref_final_head(const uint16_t* logits, int32_t* history, int history_count
     RH_CHECK(cudaMemcpy(rng_state, drng.p, sizeof(uint64_t), cudaMemcpyDeviceToHost));
     if (flags & 4) RH_CHECK(cudaMemcpy(history + generation_index, dh.as<int32_t>() + generation_index, sizeof(int32_t),
                                        cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+// ---- the code predictor's one-row kernels (fixed shapes: hidden 1024, SwiGLU 3072, 16 / 8 heads of 128,
+// caches [8][16][128]).  One call = one launch with the launcher's grid, block and shared-memory size.
+
+int qmref_predictor_qkv_m1(const uint16_t* input, const uint16_t* q_w, const uint16_t* k_w, const uint16_t* v_w, uint16_t* q_out,
+                           uint16_t* k_out, uint16_t* v_out) {
+    constexpr int H = rp::kHidden, QD = rp::kQueryDim, KD = rp::kKvDim;
+    DevBuf di, dqw, dkw, dvw, dq, dk, dv;
+    RH_CHECK(di.alloc(H * 2)); RH_CHECK(dqw.alloc((size_t)QD * H * 2)); RH_CHECK(dkw.alloc((size_t)KD * H * 2));
+    RH_CHECK(dvw.alloc((size_t)KD * H * 2)); RH_CHECK(dq.alloc(QD * 2)); RH_CHECK(dk.alloc(KD * 2)); RH_CHECK(dv.alloc(KD * 2));
+    RH_CHECK(cudaMemcpy(di.p, input, di.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dqw.p, q_w, dqw.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dkw.p, k_w, dkw.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dvw.p, v_w, dvw.bytes, cudaMemcpyHostToDevice));
+    const int total = QD + 2 * KD;
+    QINGMING_CUDA_LAUNCH(rp::predictor_qkv_m1_fused_kernel, dim3((unsigned)((total + 15) / 16)), dim3(rp::kThreads), (size_t)H * 2,
+                         (cudaStream_t) nullptr, di.as<uint16_t>(), dqw.as<uint16_t>(), dkw.as<uint16_t>(), dvw.as<uint16_t>(),
+                         dq.as<uint16_t>(), dk.as<uint16_t>(), dv.as<uint16_t>());
+    RH_CHECK(cudaGetLastError());
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(q_out, dq.p, dq.bytes, cudaMemcpyDeviceToHost));
+    RH_CHECK(cudaMemcpy(k_out, dk.p, dk.bytes, cudaMemcpyDeviceToHost));
+    RH_CHECK(cudaMemcpy(v_out, dv.p, dv.bytes, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+// caches are host arrays [8][16][128], updated in place at cache_position; cosine / sine: that position's 128-entry row.
+int qmref_predictor_qk_norm_rope_cache_m1(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* q_norm_w,
+                                          const uint16_t* k_norm_w, const uint16_t* cosine, const uint16_t* sine, uint16_t* q_rot,
+                                          uint16_t* key_cache, uint16_t* value_cache, int cache_position) {
+    constexpr int QD = rp::kQueryDim, KD = rp::kKvDim;
+    const size_t cb = (size_t)rp::kKvHeads * rp::kMaxCache * kD * 2;
+    DevBuf dq, dk, dv, dqw, dkw, dc, ds, dqr, dkc, dvc;
+    RH_CHECK(dq.alloc(QD * 2)); RH_CHECK(dk.alloc(KD * 2)); RH_CHECK(dv.alloc(KD * 2)); RH_CHECK(dqw.alloc(kD * 2));
+    RH_CHECK(dkw.alloc(kD * 2)); RH_CHECK(dc.alloc(kD * 2)); RH_CHECK(ds.alloc(kD * 2)); RH_CHECK(dqr.alloc(QD * 2));
+    RH_CHECK(dkc.alloc(cb)); RH_CHECK(dvc.alloc(cb));
+    RH_CHECK(cudaMemcpy(dq.p, q, dq.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dk.p, k, dk.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dv.p, v, dv.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dqw.p, q_norm_w, kD * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dkw.p, k_norm_w, kD * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dc.p, cosine, kD * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(ds.p, sine, kD * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dkc.p, key_cache, cb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dvc.p, value_cache, cb, cudaMemcpyHostToDevice));
+    QINGMING_CUDA_LAUNCH(rp::predictor_qk_norm_rope_cache_m1_kernel, dim3((unsigned)(rp::kQueryHeads + rp::kKvHeads)), dim3(rp::kThreads),
+                         0, (cudaStream_t) nullptr, dq.as<uint16_t>(), dk.as<uint16_t>(), dv.as<uint16_t>(), dqw.as<uint16_t>(),
+                         dkw.as<uint16_t>(), dc.as<uint16_t>(), ds.as<uint16_t>(), dqr.as<uint16_t>(), dkc.as<uint16_t>(),
+                         dvc.as<uint16_t>(), cache_position);
+    RH_CHECK(cudaGetLastError());
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(q_rot, dqr.p, dqr.bytes, cudaMemcpyDeviceToHost));
+    RH_CHECK(cudaMemcpy(key_cache, dkc.p, cb, cudaMemcpyDeviceToHost));
+    RH_CHECK(cudaMemcpy(value_cache, dvc.p, cb, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int qmref_predictor_attention_m1(const uint16_t* q_rot, const uint16_t* key_cache, const uint16_t* value_cache, uint16_t* context,
+                                 int key_length) {
+    constexpr int QD = rp::kQueryDim;
+    const size_t cb = (size_t)rp::kKvHeads * rp::kMaxCache * kD * 2;
+    if (key_length < 1 || key_length > rp::kMaxCache) return -2;
+    DevBuf dq, dkc, dvc, dctx;
+    RH_CHECK(dq.alloc(QD * 2)); RH_CHECK(dkc.alloc(cb)); RH_CHECK(dvc.alloc(cb)); RH_CHECK(dctx.alloc(QD * 2));
+    RH_CHECK(cudaMemcpy(dq.p, q_rot, dq.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dkc.p, key_cache, cb, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dvc.p, value_cache, cb, cudaMemcpyHostToDevice));
+    QINGMING_CUDA_LAUNCH(rp::predictor_attention_gqa2_m1_kernel, dim3((unsigned)rp::kKvHeads), dim3(rp::kThreads), 0,
+                         (cudaStream_t) nullptr, dq.as<uint16_t>(), dkc.as<uint16_t>(), dvc.as<uint16_t>(), dctx.as<uint16_t>(), key_length);
+    RH_CHECK(cudaGetLastError());
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(context, dctx.p, dctx.bytes, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+// out[n] = dot(input, weight[n]) (+ residual[n]); weight [n_dim][k_dim]; residual may be null.
+int qmref_predictor_linear_m1(const uint16_t* input, const uint16_t* weight, const uint16_t* residual, uint16_t* out, int n_dim,
+                              int k_dim) {
+    DevBuf di, dw, dr, dout;
+    RH_CHECK(di.alloc((size_t)k_dim * 2)); RH_CHECK(dw.alloc((size_t)n_dim * k_dim * 2)); RH_CHECK(dr.alloc((size_t)n_dim * 2));
+    RH_CHECK(dout.alloc((size_t)n_dim * 2));
+    RH_CHECK(cudaMemcpy(di.p, input, di.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dw.p, weight, dw.bytes, cudaMemcpyHostToDevice));
+    if (residual) RH_CHECK(cudaMemcpy(dr.p, residual, dr.bytes, cudaMemcpyHostToDevice));
+    QINGMING_CUDA_LAUNCH(rp::predictor_linear_m1_fused_kernel, dim3((unsigned)((n_dim + 15) / 16)), dim3(rp::kThreads), (size_t)k_dim * 2,
+                         (cudaStream_t) nullptr, di.as<uint16_t>(), dw.as<uint16_t>(), residual ? dr.as<uint16_t>() : (uint16_t*)nullptr,
+                         dout.as<uint16_t>(), n_dim, k_dim);
+    RH_CHECK(cudaGetLastError());
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(out, dout.p, dout.bytes, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int qmref_predictor_add_postnorm_m1(const uint16_t* hidden, const uint16_t* attention, const uint16_t* norm_w, uint16_t* residual,
+                                    uint16_t* normalized) {
+    constexpr int H = rp::kHidden;
+    DevBuf dh, da, dw, dr, dn;
+    RH_CHECK(dh.alloc(H * 2)); RH_CHECK(da.alloc(H * 2)); RH_CHECK(dw.alloc(H * 2)); RH_CHECK(dr.alloc(H * 2)); RH_CHECK(dn.alloc(H * 2));
+    RH_CHECK(cudaMemcpy(dh.p, hidden, H * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(da.p, attention, H * 2, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dw.p, norm_w, H * 2, cudaMemcpyHostToDevice));
+    QINGMING_CUDA_LAUNCH(rp::predictor_add_postnorm_m1_kernel, dim3(1), dim3(rp::kThreads), 0, (cudaStream_t) nullptr, dh.as<uint16_t>(),
+                         da.as<uint16_t>(), dw.as<uint16_t>(), dr.as<uint16_t>(), dn.as<uint16_t>());
+    RH_CHECK(cudaGetLastError());
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(residual, dr.p, H * 2, cudaMemcpyDeviceToHost));
+    RH_CHECK(cudaMemcpy(normalized, dn.p, H * 2, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int qmref_predictor_gate_up_swiglu_m1(const uint16_t* input, const uint16_t* gate_w, const uint16_t* up_w, uint16_t* out) {
+    constexpr int H = rp::kHidden, I = rp::kIntermediate;
+    DevBuf di, dg, du, dout;
+    RH_CHECK(di.alloc(H * 2)); RH_CHECK(dg.alloc((size_t)I * H * 2)); RH_CHECK(du.alloc((size_t)I * H * 2)); RH_CHECK(dout.alloc(I * 2));
+    RH_CHECK(cudaMemcpy(di.p, input, di.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(dg.p, gate_w, dg.bytes, cudaMemcpyHostToDevice));
+    RH_CHECK(cudaMemcpy(du.p, up_w, du.bytes, cudaMemcpyHostToDevice));
+    QINGMING_CUDA_LAUNCH(rp::predictor_gate_up_swiglu_m1_kernel, dim3((unsigned)((I + 15) / 16)), dim3(rp::kThreads), (size_t)H * 2,
+                         (cudaStream_t) nullptr, di.as<uint16_t>(), dg.as<uint16_t>(), du.as<uint16_t>(), dout.as<uint16_t>());
+    RH_CHECK(cudaGetLastError());
+    RH_CHECK(cudaDeviceSynchronize());
+    RH_CHECK(cudaMemcpy(out, dout.p, dout.bytes, cudaMemcpyDeviceToHost));
     return 0;
 }
 

@@ -168,13 +168,24 @@ def decode_case(qm, tmp_path, lengths, shuffle_pages, seed):
     got, pools, _ = results[0]
     m = oracle.error_metrics(oracle.bf16_to_f32(got), oracle.bf16_to_f32(want))
     assert m["max_abs"] <= 8e-2 and m["mean_rel"] <= 2e-2, m
-    # layer 0's appended rows see exactly the oracle's inputs: V rows are bit copies, K rows within a bf16 ulp or two
+    # layer 0's appended rows land where the page table says; their values come from the tensor-core projections,
+    # which differ from the oracle's lane-strided sums by a bf16 ulp here and there
     for s in range(b):
         pos = int(sc0.lengths[s])
         page, slot = table[s, pos // 64], pos % 64
-        assert np.array_equal(pools[0][1][page, :, slot], expected_rows[0][s][1])
+        dv = np.abs(oracle.bf16_to_f32(pools[0][1][page, :, slot]) - oracle.bf16_to_f32(expected_rows[0][s][1]))
         dk = np.abs(oracle.bf16_to_f32(pools[0][0][page, :, slot]) - oracle.bf16_to_f32(expected_rows[0][s][0]))
-        assert dk.max() <= 2.0 ** -5
+        assert dv.max() <= 2.0 ** -4 and dk.max() <= 2.0 ** -4
+        assert (pools[0][1][page, :, slot] == expected_rows[0][s][1]).mean() >= 0.85
+    # and nothing else in the pools moved: every other row is what was uploaded
+    for layer, sc in enumerate(scs):
+        for which, name in ((0, "kpool"), (1, "vpool")):
+            before = np.fromfile(tmp_path / f"{name}{layer}.bin", dtype=np.uint16).reshape(sc0.num_pages, HKV, 64, D)
+            after = pools[layer][which].copy()
+            for s in range(b):
+                pos = int(sc0.lengths[s])
+                after[table[s, pos // 64], :, pos % 64] = before[table[s, pos // 64], :, pos % 64]
+            assert np.array_equal(after, before)
     # the profiled run reports the reference's buckets, each one measured
     text = results[1][2]
     keys = json.loads([line for line in text.splitlines() if line.startswith("{")][-1])
@@ -248,15 +259,16 @@ def test_cpp_prefill_two_layers_packed_varlen(qm, tmp_path):
     assert m["max_abs"] <= 8e-2 and m["mean_rel"] <= 2e-2, m
     got_last = np.fromfile(tmp_path / "out_last.bin", dtype=np.uint16).reshape(b, hidden)
     assert np.array_equal(got_last, got[last])
-    # layer 0's cache is written from exactly the oracle's inputs: V bit for bit, K within a bf16 ulp or two
+    # layer 0's cache holds every prompt row where the page table says (values within a bf16 ulp or two of the
+    # oracle's: they come from the tensor-core projections)
     kp = np.fromfile(tmp_path / "out_kpool0.bin", dtype=np.uint16).reshape(sc0.num_pages, HKV, 64, D)
     vp = np.fromfile(tmp_path / "out_vpool0.bin", dtype=np.uint16).reshape(sc0.num_pages, HKV, 64, D)
     for s in range(b):
         n = int(lengths[s])
         kc, vc = caches[0][s]
-        assert np.array_equal(oracle.gather_paged(vp, table[s], n, sc0.max_cache)[:, :n], vc[:, :n])
+        dv = np.abs(oracle.bf16_to_f32(oracle.gather_paged(vp, table[s], n, sc0.max_cache)[:, :n]) - oracle.bf16_to_f32(vc[:, :n]))
         dk = np.abs(oracle.bf16_to_f32(oracle.gather_paged(kp, table[s], n, sc0.max_cache)[:, :n]) - oracle.bf16_to_f32(kc[:, :n]))
-        assert dk.max() <= 2.0 ** -4
+        assert dv.max() <= 2.0 ** -4 and dk.max() <= 2.0 ** -4
 
 
 @pytest.mark.gpu
