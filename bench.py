@@ -558,6 +558,7 @@ def run_ours(args):
             "decode_parity_ok": line.get("parity", {}).get("ok"),
             "prefill_tflops": pf.get("tflops"), "prefill_parity_ok": pf.get("parity", {}).get("ok"),
             "long_context_us": lc.get("us_per_layer"), "long_context_us_nccl": lc.get("us_per_layer_nccl_all_gather"),
+            "long_context_us_two_launch": lc.get("us_per_layer_two_launch_peer_exchange"),
             "long_context_parity_ok": lc.get("parity", {}).get("ok"),
             "talker_tok_s_all_gpus": tk.get("tokens_per_s_all_gpus", tk.get("tokens_per_s")),
             "talker_ms_per_step": tk.get("ms_per_step"),
@@ -1121,6 +1122,9 @@ def run_long_context_section(pkg, world, rank, steps):
     def layer_peer(layer):
         sh.sharded_decode_attention_peer(eng, exchange, layer, q_rot, seq_lens, page_table, out=out)
 
+    def layer_fused(layer):
+        exchange.run_fused(layer, q_rot, seq_lens, page_table, out=out)
+
     def layer_single(layer):
         eng.launch_attention(layer, q_rot, seq_lens, page_table, out=out)
 
@@ -1141,10 +1145,14 @@ def run_long_context_section(pkg, world, rank, steps):
         if exchange is not None:
             layer_peer(0)
             parity["peer_exchange_equals_nccl_bits"] = bool(torch.equal(out.view(torch.int16), via_nccl.view(torch.int16)))
+            out.zero_()
+            layer_fused(0)
+            parity["fused_exchange_equals_nccl_bits"] = bool(torch.equal(out.view(torch.int16), via_nccl.view(torch.int16)))
     else:
         layer_single(0)
         result = out.clone()
-    ok = parity.get("all_ranks_same_bits", True) and parity.get("peer_exchange_equals_nccl_bits", True)
+    ok = (parity.get("all_ranks_same_bits", True) and parity.get("peer_exchange_equals_nccl_bits", True)
+          and parity.get("fused_exchange_equals_nccl_bits", True))
     if rank == 0:
         single = eng_full.launch_attention(0, q_rot, full_lens, full_table)
         parity["max_abs_vs_single_gpu_kernel"] = max_abs_bits(result, single)
@@ -1217,10 +1225,13 @@ def run_long_context_section(pkg, world, rank, steps):
         nccl_ms = measure(layer_nccl)
         extra["us_per_layer_nccl_all_gather"] = nccl_ms * 1e3
         if exchange is not None:
-            ms = measure(layer_peer)
-            extra["exchange"] = "one kernel over peer memory (qm_attention_exchange_combine)"
+            extra["us_per_layer_two_launch_peer_exchange"] = measure(layer_peer) * 1e3
+            ms = measure(layer_fused)
+            extra["exchange"] = ("inside the split-KV kernel's launch, over peer memory (qm_decode_attention_exchange); "
+                                 "us_per_layer_two_launch_peer_exchange = partial kernel + qm_attention_exchange_combine")
             # after the timed replays the exchange must still be in step on every rank: same bits as before
-            layer_peer(0)
+            out.zero_()
+            layer_fused(0)
             still = bool(torch.equal(out.view(torch.int16), via_nccl.view(torch.int16)))
             flag = torch.tensor([1 if still else 0], device="cuda")
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)

@@ -261,6 +261,21 @@ int32_t qm_attention_exchange_combine(qm_kv_pool* pool, const float* local_parti
                                       int32_t world, int32_t rank, int32_t rows, int32_t rows_capacity, uint16_t* out,
                                       void* stream);
 
+/* The split-KV kernel and the exchange in ONE launch, for the same streams-split-across-GPUs case.  No counterpart in
+ * the reference.  Same inputs as qm_decode_attention_partial (this pool holds a slice of every stream,
+ * local_seq_lens[s] of its keys; 0 is fine) and the same exchange buffers as qm_attention_exchange_combine.  The CTA
+ * that finishes a (stream, KV head) segment of this rank holds its two rows' partial state in registers: it stores
+ * them straight into every rank's exchange buffer, waits (bounded, QM_DEVSTAT_TIMEOUT) for the same two rows from
+ * every other rank and folds them in rank order into out [batch][q_heads][128] - no partial buffer, no second
+ * launch, and the NVLink round trip of the early segments overlaps the streaming of the late ones.  Bits equal
+ * qm_decode_attention_partial + qm_attention_exchange_combine (and + all-gather + qm_attention_combine).  Every
+ * rank calls it at the same point of its stream with the same batch; batch * q_heads <= rows_capacity, batch <= 256.
+ * The two exchange entry points may be mixed freely on one set of buffers. */
+int32_t qm_decode_attention_exchange(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const int32_t* local_seq_lens,
+                                     const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads,
+                                     uint16_t* out, void* const* peer_buffers_dev, int32_t world, int32_t rank,
+                                     int32_t rows_capacity, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* The exchange buffers as an object, for hosts that have no symmetric-memory allocator of their own.  No counterpart
  * in the reference.  qm_exchange_create allocates and zeroes this rank's buffer on the current device.  With one
  * process per GPU, every rank exports its buffer with qm_exchange_ipc_handle (QM_IPC_HANDLE_BYTES bytes, a CUDA IPC
@@ -282,6 +297,11 @@ int32_t qm_exchange_set_peers(qm_exchange* exchange, void* const* peer_buffers);
 int32_t qm_exchange_reset(qm_exchange* exchange, void* stream);
 int32_t qm_exchange_combine(qm_kv_pool* pool, qm_exchange* exchange, const float* local_partials, int32_t rows,
                             uint16_t* out, void* stream);
+/* qm_decode_attention_exchange on these buffers. */
+int32_t qm_exchange_decode_attention(qm_kv_pool* pool, qm_exchange* exchange, int32_t layer, const uint16_t* q_rot,
+                                     const int32_t* local_seq_lens, const int32_t* page_table, int32_t max_pages,
+                                     int32_t batch, int32_t q_heads, uint16_t* out, void* workspace, int64_t workspace_bytes,
+                                     void* stream);
 
 /* ---- the same exchange through NCCL, for a C++ host with one process or thread per GPU ----
  * No counterpart in the reference (single GPU; its launch_attention, 17.cu:17895, sees the whole cache). */

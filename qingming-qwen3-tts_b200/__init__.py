@@ -91,6 +91,10 @@ ABI = {
     "qm_exchange_buffer_bytes": (c_int64, [c_int32, c_int32]),
     "qm_attention_exchange_combine": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                                 c_void_p, c_void_p]),
+    "qm_decode_attention_exchange": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
+                                               c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_int64, c_void_p]),
+    "qm_exchange_decode_attention": (c_int32, [c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
+                                               c_int32, c_void_p, c_void_p, c_int64, c_void_p]),
     "qm_exchange_create": (c_int32, [c_int32, c_int32, c_int32, POINTER(c_void_p)]),
     "qm_exchange_destroy": (c_int32, [c_void_p]),
     "qm_exchange_local_buffer": (c_void_p, [c_void_p]),

@@ -29,6 +29,7 @@
 #include <cstdlib>
 #include <mutex>
 
+#include "qm_exchange_layout.cuh"
 #include "qm_norm_rope.cuh"
 
 namespace {
@@ -72,8 +73,10 @@ struct DecodeArgs {
     int kv_heads;
     int max_pages;
     int num_pages;
-    int mode;
+    int mode;                // 0: bf16 context; 1: partial state of this pool's keys; 2: partial state exchanged with
+                             //    the other ranks' and folded here (keys split across GPUs), bf16 context
     int prefetch_units;      // units per CTA whose tiles are prefetched into L2 before the dependency wait
+    ExchangeView exchange;   // mode 2: every rank's exchange buffer
 };
 
 struct SharedLayout {
@@ -88,7 +91,8 @@ struct SharedLayout {
     static constexpr int kMetaOff = kQOff + kStages * kStagingBytes;
     static constexpr int kBarOff = kMetaOff + kStages * 32;
     static constexpr int kFlagOff = kBarOff + 3 * kStages * 8;
-    static constexpr int kTotal = kFlagOff + 16;
+    static constexpr int kExchangeOff = kFlagOff + 16;           // uint32[2][2]: per query head, for the fused exchange
+    static constexpr int kTotal = kExchangeOff + 16;
 };
 
 __device__ __forceinline__ int clamp_len(int len, int max_pages, uint32_t* status) {
@@ -242,9 +246,21 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
         first_units_known = false;
     }
 
-    // Streams with nothing to attend get a zero row (mode 0) or an empty partial (mode 1).
+    // Streams with nothing to attend get a zero row (mode 0) or an empty partial (mode 1); in mode 2 the empty
+    // partial takes part in the exchange like any other (the other ranks wait for this rank's copy of every row).
+    volatile uint32_t* exchange_words = reinterpret_cast<volatile uint32_t*>(smem + SharedLayout::kExchangeOff);
     for (int s = blockIdx.x; s < a.batch; s += gridDim.x) {
         if (prefix[s + 1] != prefix[s]) continue;
+        if (a.mode == 2) {
+            if (tid < kHeadDim) {        // warps 0-3, one row after the other
+                for (int h = 0; h < 2 * hkv; ++h) {
+                    const int row = s * (2 * hkv) + h;
+                    exchange_row(a.exchange, row, tid, -CUDART_INF_F, 0.0f, 0.0f, true, a.out + (size_t)row * kHeadDim, a.status,
+                                 exchange_words, [] { named_bar_sync(2, kHeadDim); });
+                }
+            }
+            continue;
+        }
         for (int i = tid; i < 2 * hkv * kHeadDim; i += kDecodeThreads) {
             const size_t row = (size_t)s * (2 * hkv) + i / kHeadDim;
             const int d = i % kHeadDim;
@@ -585,7 +601,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                 // and the unit description may be a stale one, so it writes nothing to global memory and takes
                 // no part in the arrival count; the barriers below are still passed by everyone.
                 if (whole) {
-                    if (dead) {
+                    if (a.mode == 2) {
+                        // this CTA saw all of this rank's keys of the segment: its state is the rank's partial
+                        exchange_row(a.exchange, (int)row, d, m * kLn2, lsum, sum, !dead, a.out + row * kHeadDim, a.status,
+                                     exchange_words + 2 * qh, [qh] { named_bar_sync(2 + qh, kHeadDim); });
+                    } else if (dead) {
                     } else if (a.mode == 0) {
                         a.out[row * kHeadDim + d] = (uint16_t)f32_to_bf16_bits(sum / lsum);
                     } else {
@@ -621,7 +641,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                         *fold_flag = is_last;
                     }
                     named_bar_sync(1, kConsumerThreads);
-                    if (*fold_flag && !dead) {
+                    if (*fold_flag) {
                         __threadfence();
                         // Piece i of the segment sits in slot (c_first + i + seg).  The loads of a batch are issued
                         // together (a rolled loop would pay one L2 round trip per piece, twice); the arithmetic stays
@@ -630,7 +650,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                         const float* first = a.ws_partials + ((size_t)(c_first + seg) * 2 + qh) * kPartialStride;
                         constexpr size_t kNext = 2 * kPartialStride;
                         float big = -CUDART_INF_F;
-                        for (int i0 = 0; i0 < pieces; i0 += 8) {
+                        for (int i0 = 0; i0 < pieces && !dead; i0 += 8) {
                             float mv[8];
 #pragma unroll
                             for (int j = 0; j < 8; ++j) mv[j] = i0 + j < pieces ? __ldcg(first + (size_t)(i0 + j) * kNext) : -CUDART_INF_F;
@@ -638,7 +658,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                             for (int j = 0; j < 8; ++j) big = fmaxf(big, mv[j]);
                         }
                         float acc = 0.0f, denom = 0.0f;
-                        for (int i0 = 0; i0 < pieces; i0 += 4) {
+                        for (int i0 = 0; i0 < pieces && !dead; i0 += 4) {
                             float mv[4], lv[4], ov[4];
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
@@ -656,7 +676,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                                 }
                             }
                         }
-                        if (a.mode == 0) {
+                        if (a.mode == 2) {
+                            exchange_row(a.exchange, (int)row, d, big * kLn2, denom, acc, !dead, a.out + row * kHeadDim, a.status,
+                                         exchange_words + 2 * qh, [qh] { named_bar_sync(2 + qh, kHeadDim); });
+                        } else if (dead) {
+                        } else if (a.mode == 0) {
                             a.out[row * kHeadDim + d] = (uint16_t)f32_to_bf16_bits(acc / denom);
                         } else {
                             float* out_partial = a.partial_out + row * kPartialStride;
@@ -939,11 +963,19 @@ int decode_prefetch_units() {
 int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const int32_t* seq_lens,
                    const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads, uint16_t* out,
                    float* partial_out, void* workspace, int64_t workspace_bytes, cudaStream_t stream, int mode,
-                   const FusedInputs* fused = nullptr) {
+                   const FusedInputs* fused = nullptr, const ExchangeView* exchange = nullptr) {
     if (!pool) return qm_fail(QM_EINVAL, "pool is null");
     if (layer < 0 || layer >= pool->layers) return qm_fail(QM_EINVAL, "layer out of range");
-    if (!q_rot || !seq_lens || !page_table || !workspace || (mode == 0 ? !out : !partial_out))
+    if (!q_rot || !seq_lens || !page_table || !workspace || (mode == 1 ? !partial_out : !out))
         return qm_fail(QM_EINVAL, "null tensor pointer");
+    if (mode == 2) {
+        if (!exchange || !exchange->peers) return qm_fail(QM_EINVAL, "null pointer");
+        if (exchange->world < 1 || exchange->world > kExchangeMaxWorld || exchange->rank < 0 || exchange->rank >= exchange->world ||
+            (long long)batch * q_heads > exchange->rows_capacity)
+            return qm_fail(QM_EINVAL, "invalid exchange geometry");
+        if (batch > kMaxBatchPerLaunch)
+            return qm_fail(QM_ECAPACITY, "the fused exchange takes at most 256 streams per call");
+    }
     if (q_heads != 2 * pool->kv_heads)
         return qm_fail(QM_EINVAL, "decode attention needs q_heads == 2 * kv_heads (GQA group of 2)");
     if (batch < 0 || max_pages < 1) return qm_fail(QM_EINVAL, "invalid geometry");
@@ -979,6 +1011,7 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
     a.num_pages = pool->num_pages;
     a.mode = mode;
     a.prefetch_units = decode_prefetch_units();
+    if (exchange) a.exchange = *exchange;
     if (fused) {
         a.q_norm_weight = fused->q_norm_weight;
         a.k_norm_weight = fused->k_norm_weight;
@@ -1000,7 +1033,7 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
             a.raw_k = fused->k + (size_t)begin * pool->kv_heads * kHeadDim;
             a.raw_v = fused->v + (size_t)begin * pool->kv_heads * kHeadDim;
         }
-        if (max_pages == 1) {
+        if (max_pages == 1 && mode != 2) {
             // every stream fits one page: one small CTA per (stream, kv head), no scratch involved
             const dim3 short_grid((unsigned)(n * pool->kv_heads));
             if (fused) {
@@ -1073,6 +1106,19 @@ int32_t qm_decode_attention_partial(qm_kv_pool* pool, int32_t layer, const uint1
                                     int64_t workspace_bytes, void* stream) {
     return run_decode(pool, layer, q_rot, seq_lens, page_table, max_pages, batch, q_heads, nullptr, partial,
                       workspace, workspace_bytes, static_cast<cudaStream_t>(stream), 1);
+}
+
+int32_t qm_decode_attention_exchange(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const int32_t* local_seq_lens,
+                                     const int32_t* page_table, int32_t max_pages, int32_t batch, int32_t q_heads,
+                                     uint16_t* out, void* const* peer_buffers_dev, int32_t world, int32_t rank,
+                                     int32_t rows_capacity, void* workspace, int64_t workspace_bytes, void* stream) {
+    ExchangeView view{};
+    view.peers = reinterpret_cast<unsigned char* const*>(peer_buffers_dev);
+    view.world = world;
+    view.rank = rank;
+    view.rows_capacity = rows_capacity;
+    return run_decode(pool, layer, q_rot, local_seq_lens, page_table, max_pages, batch, q_heads, out, nullptr, workspace,
+                      workspace_bytes, static_cast<cudaStream_t>(stream), 2, nullptr, &view);
 }
 
 int32_t qm_attention_combine(const float* partials, int32_t parts, int32_t rows, uint16_t* out, void* stream) {

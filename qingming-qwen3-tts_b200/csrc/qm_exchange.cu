@@ -17,43 +17,26 @@
 //
 // Also here: the exchange object that owns such a buffer and maps the peers' buffers through CUDA IPC handles (for
 // hosts with one process per GPU) or takes peer pointers directly (one process driving several GPUs).
-#include <math_constants.h>
-
 #include <cstring>
 #include <new>
 
-#include "qm_common.cuh"
+#include "qm_exchange_layout.cuh"
 
 namespace {
 
-constexpr int kPartialWidth = kHeadDim + 2;        // m, l, o[128]
-constexpr int kExchangeThreads = 160;              // 130 payload lanes, rounded up to warps
-constexpr uint32_t kExchangeSpinLimit = 1u << 20;
-constexpr int kMaxWorld = 32;
+constexpr int kPartialWidth = kExchangeWidth;      // m, l, o[128]
+constexpr int kExchangeThreads = 128;              // one thread per output dimension of the row
+constexpr int kMaxWorld = kExchangeMaxWorld;
 
 struct ExchangeArgs {
     const float* local;              // [rows][130] this rank's partials (m in natural-log domain)
-    unsigned char* const* peers;     // [world] device pointers to every rank's exchange buffer (own included)
+    ExchangeView view;
     uint16_t* out;                   // [rows][128]
     uint32_t* status;
-    int world, rank, rows, rows_capacity;
 };
 
-// buffer layout:  float    payload[2][world][rows_capacity][130]
-//                 uint32_t arrived[2][world][rows_capacity]     sequence number of the payload in that slot
-//                 uint32_t calls[rows_capacity]                 how often this rank has exchanged that row
 __host__ __device__ __forceinline__ size_t payload_bytes(int world, int rows_capacity) {
-    return (size_t)2 * world * rows_capacity * kPartialWidth * sizeof(float);
-}
-__device__ __forceinline__ size_t payload_offset(const ExchangeArgs& a, int slot, int source, int row) {
-    return ((((size_t)slot * a.world + source) * a.rows_capacity + row) * kPartialWidth) * sizeof(float);
-}
-__device__ __forceinline__ size_t arrived_offset(const ExchangeArgs& a, int slot, int source, int row) {
-    return payload_bytes(a.world, a.rows_capacity) + (((size_t)slot * a.world + source) * a.rows_capacity + row) * sizeof(uint32_t);
-}
-__device__ __forceinline__ size_t calls_offset(const ExchangeArgs& a, int row) {
-    return payload_bytes(a.world, a.rows_capacity) + (size_t)2 * a.world * a.rows_capacity * sizeof(uint32_t) +
-           (size_t)row * sizeof(uint32_t);
+    return exchange_payload_bytes(world, rows_capacity);
 }
 
 __global__ void __launch_bounds__(kExchangeThreads) qm_exchange_combine_kernel(const ExchangeArgs a) {
@@ -61,67 +44,10 @@ __global__ void __launch_bounds__(kExchangeThreads) qm_exchange_combine_kernel(c
     pdl_wait();
     const int row = blockIdx.x;
     const int t = threadIdx.x;
-    __shared__ uint32_t sequence_shared;
-    __shared__ int timed_out;
-    if (t == 0) {
-        uint32_t* calls = reinterpret_cast<uint32_t*>(a.peers[a.rank] + calls_offset(a, row));
-        const uint32_t sequence = *calls + 1u;      // only this row's CTA of this rank ever touches the word
-        *calls = sequence;
-        sequence_shared = sequence;
-        timed_out = 0;
-    }
-    __syncthreads();
-    const uint32_t sequence = sequence_shared;
-    const int slot = (int)(sequence & 1u);
-
-    // my row into every rank's buffer, then its arrival word
-    if (t < kPartialWidth) {
-        const float v = a.local[(size_t)row * kPartialWidth + t];
-        for (int p = 0; p < a.world; ++p)
-            *reinterpret_cast<float*>(a.peers[p] + payload_offset(a, slot, a.rank, row) + (size_t)t * sizeof(float)) = v;
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (t < a.world) {
-        uint32_t* word = reinterpret_cast<uint32_t*>(a.peers[t] + arrived_offset(a, slot, a.rank, row));
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(word), "r"(sequence) : "memory");
-    }
-    // every source's row of this call
-    if (t < a.world) {
-        const uint32_t* word = reinterpret_cast<const uint32_t*>(a.peers[a.rank] + arrived_offset(a, slot, t, row));
-        bool ok = false;
-        for (uint32_t spin = 0; spin < kExchangeSpinLimit; ++spin) {
-            uint32_t seen;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(word) : "memory");
-            if ((int32_t)(seen - sequence) >= 0) {
-                ok = true;
-                break;
-            }
-            if (spin > 64) __nanosleep(200);
-        }
-        if (!ok) {
-            atomicOr(a.status, QM_DEVSTAT_TIMEOUT);
-            timed_out = 1;
-        }
-    }
-    __syncthreads();
-    // fold in rank order
-    if (t < kHeadDim) {
-        const unsigned char* mine = a.peers[a.rank];
-        float big = -CUDART_INF_F;
-        for (int g = 0; g < a.world; ++g)
-            big = fmaxf(big, *reinterpret_cast<const volatile float*>(mine + payload_offset(a, slot, g, row)));
-        float acc = 0.0f, denom = 0.0f;
-        for (int g = 0; g < a.world; ++g) {
-            const volatile float* src = reinterpret_cast<const volatile float*>(mine + payload_offset(a, slot, g, row));
-            const float l = src[1];
-            if (!(l > 0.0f)) continue;
-            const float w = __expf(src[0] - big);
-            denom = fmaf(w, l, denom);
-            acc = fmaf(w, src[2 + t], acc);
-        }
-        a.out[(size_t)row * kHeadDim + t] = (denom > 0.0f && !timed_out) ? (uint16_t)f32_to_bf16_bits(acc / denom) : (uint16_t)0;
-    }
+    __shared__ uint32_t shared2[2];
+    const float* mine = a.local + (size_t)row * kPartialWidth;
+    exchange_row(a.view, row, t, mine[0], mine[1], mine[2 + t], true, a.out + (size_t)row * kHeadDim, a.status, shared2,
+                 [] { __syncthreads(); });
 }
 
 // Rows one launch may carry: every row's CTA must be able to be resident at once.  A CTA spins until the same row
@@ -174,13 +100,12 @@ int32_t qm_attention_exchange_combine(qm_kv_pool* pool, const float* local_parti
         return qm_fail(QM_ECAPACITY, "more rows than can be resident on the GPU at once; exchange them in several calls");
     ExchangeArgs a{};
     a.local = local_partials;
-    a.peers = reinterpret_cast<unsigned char* const*>(peer_buffers_dev);
+    a.view.peers = reinterpret_cast<unsigned char* const*>(peer_buffers_dev);
+    a.view.world = world;
+    a.view.rank = rank;
+    a.view.rows_capacity = rows_capacity;
     a.out = out;
     a.status = pool->status_dev;
-    a.world = world;
-    a.rank = rank;
-    a.rows = rows;
-    a.rows_capacity = rows_capacity;
     QM_CUDA_TRY(qm_launch(qm_exchange_combine_kernel, dim3(rows), dim3(kExchangeThreads), 0, static_cast<cudaStream_t>(stream), a),
                 "partial exchange + combine launch");
     return QM_OK;
@@ -286,6 +211,22 @@ int32_t qm_exchange_combine(qm_kv_pool* pool, qm_exchange* ex, const float* loca
     }
     return qm_attention_exchange_combine(pool, local_partials, reinterpret_cast<void* const*>(ex->table_dev), ex->world, ex->rank,
                                          rows, ex->rows_capacity, out, stream);
+}
+
+int32_t qm_exchange_decode_attention(qm_kv_pool* pool, qm_exchange* ex, int32_t layer, const uint16_t* q_rot,
+                                     const int32_t* local_seq_lens, const int32_t* page_table, int32_t max_pages,
+                                     int32_t batch, int32_t q_heads, uint16_t* out, void* workspace, int64_t workspace_bytes,
+                                     void* stream) {
+    if (!ex) return qm_fail(QM_EINVAL, "exchange is null");
+    if (!ex->peers_known && ex->world > 1)
+        return qm_fail(QM_EINVAL, "peer buffers are not mapped yet: call qm_exchange_open_peers or qm_exchange_set_peers first");
+    if (!ex->peers_known) {
+        const int32_t rc = upload_peer_table(ex);
+        if (rc != QM_OK) return rc;
+    }
+    return qm_decode_attention_exchange(pool, layer, q_rot, local_seq_lens, page_table, max_pages, batch, q_heads, out,
+                                        reinterpret_cast<void* const*>(ex->table_dev), ex->world, ex->rank, ex->rows_capacity,
+                                        workspace, workspace_bytes, stream);
 }
 
 }  // extern "C"

@@ -103,6 +103,24 @@ class PeerExchange:
         return out
 
 
+    def run_fused(self, layer, q_rot, local_seq_lens, page_table, out=None):
+        """Split-KV kernel over this rank's slice with the exchange and the rank-order fold inside the same launch
+        (qm_decode_attention_exchange)."""
+        import torch
+
+        from . import _check, _ptr, _stream
+
+        batch = q_rot.shape[0]
+        if out is None:
+            out = torch.empty_like(q_rot)
+        ws = self.engine.workspace(batch)
+        _check(self.engine.lib.qm_decode_attention_exchange(
+            self.engine.pool, layer, _ptr(q_rot), _ptr(local_seq_lens), _ptr(page_table), page_table.shape[1], batch,
+            self.engine.q_heads, _ptr(out), _ptr(self.peer_ptrs), self.world, self.rank, self.rows_capacity, _ptr(ws),
+            ws.numel(), _stream()))
+        return out
+
+
 class IpcExchange:
     """The same exchange on buffers the library allocates itself and shares through CUDA IPC handles
     (qm_exchange_create / qm_exchange_ipc_handle / qm_exchange_open_peers): what a C++ host with one process per GPU
@@ -141,6 +159,20 @@ class IpcExchange:
         if out is None:
             out = torch.empty((partial.shape[0], partial.shape[1], HEAD_DIM), dtype=torch.bfloat16, device="cuda")
         _check(self.engine.lib.qm_exchange_combine(self.engine.pool, self.handle, _ptr(partial), rows, _ptr(out), _stream()))
+        return out
+
+    def run_fused(self, layer, q_rot, local_seq_lens, page_table, out=None):
+        import torch
+
+        from . import _check, _ptr, _stream
+
+        batch = q_rot.shape[0]
+        if out is None:
+            out = torch.empty_like(q_rot)
+        ws = self.engine.workspace(batch)
+        _check(self.engine.lib.qm_exchange_decode_attention(
+            self.engine.pool, self.handle, layer, _ptr(q_rot), _ptr(local_seq_lens), _ptr(page_table), page_table.shape[1],
+            batch, self.engine.q_heads, _ptr(out), _ptr(ws), ws.numel(), _stream()))
         return out
 
     def close(self):

@@ -64,20 +64,33 @@ def main():
         wanted.append(scenario._bits(sh.sharded_decode_attention(eng, runner, 0, qv, lens_dev, table)).copy())
     assert np.array_equal(wanted[0], bits)
     assert not np.array_equal(wanted[1], wanted[0])
+    # a call with two of the four streams splits the keys over the CTAs differently, so it has its own reference
+    first_two = (variants[2][:2].contiguous(), lens_dev[:2].contiguous(), table[:2].contiguous())
+    wanted_two = scenario._bits(sh.sharded_decode_attention(eng, runner, 0, *first_two)).copy()
 
     def check(name, call):
         for i, qv in enumerate(variants):
             got = scenario._bits(call(qv, lens_dev, table))
             assert np.array_equal(got, wanted[i]), f"{name}: call {i} differs from all-gather + combine"
         # fewer rows in one call, then all rows again: the per-row call counters keep the ranks in step
-        got = scenario._bits(call(variants[2][:2].contiguous(), lens_dev[:2].contiguous(), table[:2].contiguous()))
-        assert np.array_equal(got, wanted[2][:2]), f"{name}: two-stream call differs"
+        got = scenario._bits(call(*first_two))
+        assert np.array_equal(got, wanted_two), f"{name}: two-stream call differs"
         got = scenario._bits(call(variants[3], lens_dev, table))
         assert np.array_equal(got, wanted[3]), f"{name}: call after a smaller one differs"
 
     # 1. one kernel over torch symmetric memory
     exchange = sh.PeerExchange(eng, rows_capacity=sc.batch * 16)
     check("peer exchange", lambda qv, ln, tb_: sh.sharded_decode_attention_peer(eng, exchange, 0, qv, ln, tb_))
+    # the same exchange inside the split-KV kernel's own launch, mixed with the two-launch form on the same buffers
+    check("fused exchange", lambda qv, ln, tb_: exchange.run_fused(0, qv, ln, tb_))
+    check("peer exchange after fused", lambda qv, ln, tb_: sh.sharded_decode_attention_peer(eng, exchange, 0, qv, ln, tb_))
+    # a rank that holds no keys of a stream still takes part: stream 1's keys all on rank 0
+    lens_skewed = lens_dev.clone()
+    if rank != 0:
+        lens_skewed[1] = 0
+    want_skewed = scenario._bits(sh.sharded_decode_attention(eng, runner, 0, variants[1], lens_skewed, table)).copy()
+    got_skewed = scenario._bits(exchange.run_fused(0, variants[1], lens_skewed, table))
+    assert np.array_equal(got_skewed, want_skewed), "fused exchange with an empty slice differs"
     # ... and replayed from a CUDA graph with new inputs each time (the call number is device state)
     static_q = variants[0].clone()
     out_graph = torch.empty_like(static_q)
@@ -99,6 +112,7 @@ def main():
     # 2. the same kernel on buffers shared through CUDA IPC handles (the C++ host's route)
     ipc = sh.IpcExchange(eng, rows_capacity=sc.batch * 16)
     check("ipc exchange", lambda qv, ln, tb_: sh.sharded_decode_attention_peer(eng, ipc, 0, qv, ln, tb_))
+    check("ipc fused exchange", lambda qv, ln, tb_: ipc.run_fused(0, qv, ln, tb_))
     # 3. the C entry point that does partial -> ncclAllGather -> combine on a communicator of its own
     nccl = sh.NcclSharded(eng, sc.batch)
     for i, qv in enumerate(variants):
@@ -119,4 +133,10 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:
+        import traceback
+
+        print("SHARDED_WORKER_FAILED rank", os.environ.get("RANK"), traceback.format_exc(), flush=True)
+        raise

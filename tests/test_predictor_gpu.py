@@ -1,6 +1,7 @@
 """A code-predictor frame (reference capture_step, 17.cu:13616-13905) on the library's entry points against the same
 chain built from the oracle's operators: reduced widths (hidden 256, SwiGLU 512, 2 layers, 4 steps), real head shape
-(16 / 8 heads of 128, vocabulary 2048).  Each step's logits are compared under the chain tolerance; the oracle
+(16 / 8 heads of 128, vocabulary 2048).  Each step's logits are compared under the path's tolerance (the oracle's
+operators are pinned to the reference's predictor kernels by tests/test_predictor_golden_cpu.py); the oracle
 chain is fed the library's own codes, so a near-tie cannot send the two chains down different paths, and each code
 is checked to be exactly what the restated sampler draws from the library's logits."""
 import importlib
@@ -88,6 +89,12 @@ def test_predictor_frame_matches_oracle_chain(qm, top_k):
         want_logits = oracle.linear(oracle.rmsnorm(last, w["final_norm"]), w["heads"][step])
         m = oracle.error_metrics(oracle.bf16_to_f32(got_logits[step]), oracle.bf16_to_f32(want_logits))
         worst = {k: max(worst[k], m[k]) for k in worst}
+        scale = float(np.abs(oracle.bf16_to_f32(want_logits)).max())
+        print(f"predictor step {step}: max_abs {m['max_abs']:.4f} mean_rel {m['mean_rel']:.5f} logits up to {scale:.2f}")
+        # Per-step budget: the path's tolerance (max-abs 2e-2 for values of order one, mean-relative 1e-2), the
+        # absolute part scaled to the size of the logits - a bf16 ulp is 0.031 at 4 - since every step is
+        # teacher-forced with the library's own codes and so starts from the same inputs as the oracle's.
+        assert m["max_abs"] <= 2e-2 * max(1.0, scale / 2.0) and m["mean_rel"] <= 1e-2, (step, m, scale)
         for s in range(streams):
             # the library's code is what the restated sampler draws from the library's own logits
             code, _, state[s], _ = oracle.final_head_sample(got_logits[step][s], flags=0, top_k=top_k, temperature=0.9,
@@ -95,6 +102,6 @@ def test_predictor_frame_matches_oracle_chain(qm, top_k):
             assert code == codes[step][s], (step, s)
         row_input = w["embeddings"][step][codes[step]]            # teacher forcing with the library's codes
     print("predictor frame", worst)
-    assert worst["max_abs"] <= 1e-1 and worst["mean_rel"] <= 3e-2, worst
+    assert worst["max_abs"] <= 5e-2 and worst["mean_rel"] <= 1e-2, worst
     if top_k:
         assert [int(x) for x in states.cpu().numpy().astype(np.uint64)] == state

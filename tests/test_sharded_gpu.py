@@ -106,5 +106,5 @@ def test_real_ranks_over_nccl_when_two_gpus_are_present(qm):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29533", str(ROOT / "tests" / "sharded_worker.py")]
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
-    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert proc.returncode == 0, proc.stdout[-6000:] + proc.stderr[-1500:]
     assert "SHARDED_OK" in proc.stdout
