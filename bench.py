@@ -559,6 +559,7 @@ def run_ours(args):
             "prefill_tflops": pf.get("tflops"), "prefill_parity_ok": pf.get("parity", {}).get("ok"),
             "long_context_us": lc.get("us_per_layer"), "long_context_us_nccl": lc.get("us_per_layer_nccl_all_gather"),
             "long_context_us_two_launch": lc.get("us_per_layer_two_launch_peer_exchange"),
+            "long_context_us_fused": lc.get("us_per_layer_fused_peer_exchange"),
             "long_context_parity_ok": lc.get("parity", {}).get("ok"),
             "talker_tok_s_all_gpus": tk.get("tokens_per_s_all_gpus", tk.get("tokens_per_s")),
             "talker_ms_per_step": tk.get("ms_per_step"),
@@ -1225,10 +1226,13 @@ def run_long_context_section(pkg, world, rank, steps):
         nccl_ms = measure(layer_nccl)
         extra["us_per_layer_nccl_all_gather"] = nccl_ms * 1e3
         if exchange is not None:
-            extra["us_per_layer_two_launch_peer_exchange"] = measure(layer_peer) * 1e3
-            ms = measure(layer_fused)
-            extra["exchange"] = ("inside the split-KV kernel's launch, over peer memory (qm_decode_attention_exchange); "
-                                 "us_per_layer_two_launch_peer_exchange = partial kernel + qm_attention_exchange_combine")
+            two_launch_ms = measure(layer_peer)
+            fused_ms = measure(layer_fused)
+            extra["us_per_layer_two_launch_peer_exchange"] = two_launch_ms * 1e3
+            extra["us_per_layer_fused_peer_exchange"] = fused_ms * 1e3
+            ms = min(two_launch_ms, fused_ms)
+            extra["exchange"] = ("us_per_layer is the faster of the two peer-memory forms: fused = inside the split-KV kernel's "
+                                 "launch (qm_decode_attention_exchange), two_launch = partial kernel + qm_attention_exchange_combine")
             # after the timed replays the exchange must still be in step on every rank: same bits as before
             out.zero_()
             layer_fused(0)

@@ -92,7 +92,8 @@ struct SharedLayout {
     static constexpr int kBarOff = kMetaOff + kStages * 32;
     static constexpr int kFlagOff = kBarOff + 3 * kStages * 8;
     static constexpr int kExchangeOff = kFlagOff + 16;           // uint32[2][2]: per query head, for the fused exchange
-    static constexpr int kTotal = kExchangeOff + 16;
+    static constexpr int kPeerOff = kExchangeOff + 16;           // the ranks' exchange buffer pointers (mode 2)
+    static constexpr int kTotal = kPeerOff + kExchangeMaxWorld * 8;
 };
 
 __device__ __forceinline__ int clamp_len(int len, int max_pages, uint32_t* status) {
@@ -249,13 +250,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
     // Streams with nothing to attend get a zero row (mode 0) or an empty partial (mode 1); in mode 2 the empty
     // partial takes part in the exchange like any other (the other ranks wait for this rank's copy of every row).
     volatile uint32_t* exchange_words = reinterpret_cast<volatile uint32_t*>(smem + SharedLayout::kExchangeOff);
+    ExchangeView xview = a.exchange;
+    if (a.mode == 2) {
+        xview = exchange_cache_peers(a.exchange, reinterpret_cast<unsigned char**>(smem + SharedLayout::kPeerOff), tid);
+        __syncthreads();
+    }
     for (int s = blockIdx.x; s < a.batch; s += gridDim.x) {
         if (prefix[s + 1] != prefix[s]) continue;
         if (a.mode == 2) {
             if (tid < kHeadDim) {        // warps 0-3, one row after the other
                 for (int h = 0; h < 2 * hkv; ++h) {
                     const int row = s * (2 * hkv) + h;
-                    exchange_row(a.exchange, row, tid, -CUDART_INF_F, 0.0f, 0.0f, true, a.out + (size_t)row * kHeadDim, a.status,
+                    exchange_row(xview, row, tid, -CUDART_INF_F, 0.0f, 0.0f, true, a.out + (size_t)row * kHeadDim, a.status,
                                  exchange_words, [] { named_bar_sync(2, kHeadDim); });
                 }
             }
@@ -603,7 +609,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                 if (whole) {
                     if (a.mode == 2) {
                         // this CTA saw all of this rank's keys of the segment: its state is the rank's partial
-                        exchange_row(a.exchange, (int)row, d, m * kLn2, lsum, sum, !dead, a.out + row * kHeadDim, a.status,
+                        exchange_row(xview, (int)row, d, m * kLn2, lsum, sum, !dead, a.out + row * kHeadDim, a.status,
                                      exchange_words + 2 * qh, [qh] { named_bar_sync(2 + qh, kHeadDim); });
                     } else if (dead) {
                     } else if (a.mode == 0) {
@@ -677,7 +683,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                             }
                         }
                         if (a.mode == 2) {
-                            exchange_row(a.exchange, (int)row, d, big * kLn2, denom, acc, !dead, a.out + row * kHeadDim, a.status,
+                            exchange_row(xview, (int)row, d, big * kLn2, denom, acc, !dead, a.out + row * kHeadDim, a.status,
                                          exchange_words + 2 * qh, [qh] { named_bar_sync(2 + qh, kHeadDim); });
                         } else if (dead) {
                         } else if (a.mode == 0) {

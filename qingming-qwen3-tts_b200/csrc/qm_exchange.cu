@@ -45,9 +45,12 @@ __global__ void __launch_bounds__(kExchangeThreads) qm_exchange_combine_kernel(c
     const int row = blockIdx.x;
     const int t = threadIdx.x;
     __shared__ uint32_t shared2[2];
+    __shared__ unsigned char* peer_cache[kExchangeMaxWorld];
+    const ExchangeView view = exchange_cache_peers(a.view, peer_cache, t);
     const float* mine = a.local + (size_t)row * kPartialWidth;
-    exchange_row(a.view, row, t, mine[0], mine[1], mine[2 + t], true, a.out + (size_t)row * kHeadDim, a.status, shared2,
-                 [] { __syncthreads(); });
+    const float m = mine[0], l = mine[1], o = mine[2 + t];
+    __syncthreads();
+    exchange_row(view, row, t, m, l, o, true, a.out + (size_t)row * kHeadDim, a.status, shared2, [] { __syncthreads(); });
 }
 
 // Rows one launch may carry: every row's CTA must be able to be resident at once.  A CTA spins until the same row

@@ -15,9 +15,20 @@ constexpr uint32_t kExchangeSpinLimit = 1u << 20;
 constexpr int kExchangeMaxWorld = 32;
 
 struct ExchangeView {
-    unsigned char* const* peers;     // [world] device pointers to every rank's buffer (own included)
+    unsigned char* const* peers;     // [world] pointers to every rank's buffer (own included).  The kernels copy the
+                                     // array into shared memory first: it is read several times per row, and a
+                                     // pointer fetched from global memory costs an L2 round trip before each use.
     int world, rank, rows_capacity;
 };
+
+// Copies the peer pointer array into `cache` (shared memory, kExchangeMaxWorld entries) and returns a view on it.
+// Call from all threads of the CTA, then synchronise before the first exchange_row.
+__device__ __forceinline__ ExchangeView exchange_cache_peers(const ExchangeView& x, unsigned char** cache, int tid) {
+    if (tid < x.world && tid < kExchangeMaxWorld) cache[tid] = x.peers[tid];
+    ExchangeView cached = x;
+    cached.peers = cache;
+    return cached;
+}
 
 __host__ __device__ __forceinline__ size_t exchange_payload_bytes(int world, int rows_capacity) {
     return (size_t)2 * world * rows_capacity * kExchangeWidth * sizeof(float);
@@ -67,7 +78,9 @@ __device__ __forceinline__ void exchange_row(const ExchangeView& x, int row, int
             }
         }
     }
-    __threadfence_system();
+    // The group's barrier orders every thread's payload stores before the stores below; the release at system scope
+    // is cumulative over what the storing thread has observed through that barrier, so one fence per arrival word
+    // (not one per payload thread) publishes the whole row.
     sync();
     if (t < x.world && live) {
         uint32_t* word = reinterpret_cast<uint32_t*>(x.peers[t] + exchange_arrived_offset(x, slot, x.rank, row));

@@ -106,10 +106,11 @@ def test_cpp_code_predictor_frame_matches_oracle_chain(qm, tmp_path, top_k):
             want = oracle.linear(oracle.rmsnorm(last, w["final_norm"]), w["heads"][step])
             m = oracle.error_metrics(oracle.bf16_to_f32(logits[step]), oracle.bf16_to_f32(want))
             print(f"{mode} step {step}: max_abs {m['max_abs']:.4f} mean_rel {m['mean_rel']:.5f}")
-            # per-step budget: the path's tolerance, the absolute part scaled to the size of the logits (a bf16 ulp
-            # is 0.031 at 4); every step is teacher-forced with the driver's own codes
+            # per-step budget: the path's mean-relative tolerance (1e-2), and at most 5e-2 absolute on logits that
+            # reach 4 (a bf16 ulp is 0.016 at 2 and 0.031 at 4; two layers of one-ulp differences add up to two or
+            # three); every step is teacher-forced with the driver's own codes
             scale = float(np.abs(oracle.bf16_to_f32(want)).max())
-            assert m["max_abs"] <= 2e-2 * max(1.0, scale / 2.0) and m["mean_rel"] <= 1e-2, (mode, step, m, scale)
+            assert m["max_abs"] <= 5e-2 and m["mean_rel"] <= 1e-2, (mode, step, m, scale)
             for s in range(streams):
                 code, _, state[s], _ = oracle.final_head_sample(logits[step][s], flags=0, top_k=top_k, temperature=0.9, rng_state=state[s])
                 assert code == codes[step][s], (mode, step, s)

@@ -91,10 +91,10 @@ def test_predictor_frame_matches_oracle_chain(qm, top_k):
         worst = {k: max(worst[k], m[k]) for k in worst}
         scale = float(np.abs(oracle.bf16_to_f32(want_logits)).max())
         print(f"predictor step {step}: max_abs {m['max_abs']:.4f} mean_rel {m['mean_rel']:.5f} logits up to {scale:.2f}")
-        # Per-step budget: the path's tolerance (max-abs 2e-2 for values of order one, mean-relative 1e-2), the
-        # absolute part scaled to the size of the logits - a bf16 ulp is 0.031 at 4 - since every step is
-        # teacher-forced with the library's own codes and so starts from the same inputs as the oracle's.
-        assert m["max_abs"] <= 2e-2 * max(1.0, scale / 2.0) and m["mean_rel"] <= 1e-2, (step, m, scale)
+        # Per-step budget: the path's mean-relative tolerance (1e-2), and at most 5e-2 absolute on logits that reach
+        # 4 (a bf16 ulp is 0.016 at 2 and 0.031 at 4; two layers of one-ulp differences add up to two or three).
+        # Every step is teacher-forced with the library's own codes and so starts from the oracle's inputs.
+        assert m["max_abs"] <= 5e-2 and m["mean_rel"] <= 1e-2, (step, m, scale)
         for s in range(streams):
             # the library's code is what the restated sampler draws from the library's own logits
             code, _, state[s], _ = oracle.final_head_sample(got_logits[step][s], flags=0, top_k=top_k, temperature=0.9,
