@@ -106,7 +106,7 @@ __device__ __forceinline__ int clamp_len(int len, int max_pages, uint32_t* statu
     return len;
 }
 
-template <bool kFused>
+template <bool kFused, bool kExchange = false>
 __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(const DecodeArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     int32_t* prefix = reinterpret_cast<int32_t*>(smem + SharedLayout::kPrefixOff);
@@ -251,13 +251,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
     // partial takes part in the exchange like any other (the other ranks wait for this rank's copy of every row).
     volatile uint32_t* exchange_words = reinterpret_cast<volatile uint32_t*>(smem + SharedLayout::kExchangeOff);
     ExchangeView xview = a.exchange;
-    if (a.mode == 2) {
+    if (kExchange) {
         xview = exchange_cache_peers(a.exchange, reinterpret_cast<unsigned char**>(smem + SharedLayout::kPeerOff), tid);
         __syncthreads();
     }
     for (int s = blockIdx.x; s < a.batch; s += gridDim.x) {
         if (prefix[s + 1] != prefix[s]) continue;
-        if (a.mode == 2) {
+        if (kExchange) {
             if (tid < kHeadDim) {        // warps 0-3, one row after the other
                 for (int h = 0; h < 2 * hkv; ++h) {
                     const int row = s * (2 * hkv) + h;
@@ -607,10 +607,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                 // and the unit description may be a stale one, so it writes nothing to global memory and takes
                 // no part in the arrival count; the barriers below are still passed by everyone.
                 if (whole) {
-                    if (a.mode == 2) {
+                    if (kExchange) {
                         // this CTA saw all of this rank's keys of the segment: its state is the rank's partial
                         exchange_row(xview, (int)row, d, m * kLn2, lsum, sum, !dead, a.out + row * kHeadDim, a.status,
-                                     exchange_words + 2 * qh, [qh] { named_bar_sync(2 + qh, kHeadDim); });
+                                     exchange_words + 2 * qh, [qh] { if (qh) named_bar_sync(3, kHeadDim); else named_bar_sync(2, kHeadDim); });
                     } else if (dead) {
                     } else if (a.mode == 0) {
                         a.out[row * kHeadDim + d] = (uint16_t)f32_to_bf16_bits(sum / lsum);
@@ -647,7 +647,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                         *fold_flag = is_last;
                     }
                     named_bar_sync(1, kConsumerThreads);
-                    if (*fold_flag) {
+                    if (*fold_flag && (kExchange || !dead)) {
                         __threadfence();
                         // Piece i of the segment sits in slot (c_first + i + seg).  The loads of a batch are issued
                         // together (a rolled loop would pay one L2 round trip per piece, twice); the arithmetic stays
@@ -682,9 +682,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                                 }
                             }
                         }
-                        if (a.mode == 2) {
+                        if (kExchange) {
                             exchange_row(xview, (int)row, d, big * kLn2, denom, acc, !dead, a.out + row * kHeadDim, a.status,
-                                         exchange_words + 2 * qh, [qh] { named_bar_sync(2 + qh, kHeadDim); });
+                                         exchange_words + 2 * qh, [qh] { if (qh) named_bar_sync(3, kHeadDim); else named_bar_sync(2, kHeadDim); });
                         } else if (dead) {
                         } else if (a.mode == 0) {
                             a.out[row * kHeadDim + d] = (uint16_t)f32_to_bf16_bits(acc / denom);
@@ -999,6 +999,9 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
         QM_CUDA_TRY(cudaFuncSetAttribute(qm_decode_splitkv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SharedLayout::kTotal),
                     "raise decode kernel shared memory");
+        QM_CUDA_TRY(cudaFuncSetAttribute(qm_decode_splitkv_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SharedLayout::kTotal),
+                    "raise decode kernel shared memory");
         attr_device = pool->device;
     }
     int grid = 2 * pool->sm_count;
@@ -1051,7 +1054,12 @@ int32_t run_decode(qm_kv_pool* pool, int32_t layer, const uint16_t* q_rot, const
             }
             continue;
         }
-        if (fused) {
+        if (mode == 2) {
+            // the exchange is a variant of its own, so that the other modes compile without it
+            QM_CUDA_TRY(qm_launch(qm_decode_splitkv_kernel<false, true>, dim3(grid), dim3(kDecodeThreads), SharedLayout::kTotal,
+                                  stream, a),
+                        "split-KV decode attention with exchange launch");
+        } else if (fused) {
             QM_CUDA_TRY(qm_launch(qm_decode_splitkv_kernel<true>, dim3(grid), dim3(kDecodeThreads), SharedLayout::kTotal,
                                   stream, a),
                         "fused decode step launch");
