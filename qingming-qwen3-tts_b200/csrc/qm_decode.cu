@@ -407,17 +407,15 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) qm_decode_splitkv_kernel(co
                 if (new_segment || last_page) {
                     const uint2 craw = *reinterpret_cast<const uint2*>(staging + 512 + lane * 8);
                     const uint2 sraw = *reinterpret_cast<const uint2*>(staging + 768 + lane * 8);
-                    const float c[4] = {bf16_lo(craw.x), bf16_hi(craw.x), bf16_lo(craw.y), bf16_hi(craw.y)};
-                    const float sn[4] = {bf16_lo(sraw.x), bf16_hi(sraw.x), bf16_lo(sraw.y), bf16_hi(sraw.y)};
                     if (new_segment) {
 #pragma unroll
                         for (int h2 = 0; h2 < 2; ++h2) {
                             uint2* row = reinterpret_cast<uint2*>(staging + h2 * 256 + lane * 8);
-                            *row = norm_rope_row(*row, wq, c, sn, lane, a.epsilon);
+                            *row = norm_rope_row(*row, wq, craw, sraw, lane, a.epsilon);
                         }
                     }
                     if (last_page && nvalid > 0 && !dead) {      // after a wait that gave up nothing here is trustworthy: no stores
-                        const uint2 krow = norm_rope_row(*reinterpret_cast<const uint2*>(staging + 1024 + lane * 8), wk, c, sn,
+                        const uint2 krow = norm_rope_row(*reinterpret_cast<const uint2*>(staging + 1024 + lane * 8), wk, craw, sraw,
                                                          lane, a.epsilon);
                         const uint2 vrow = *reinterpret_cast<const uint2*>(staging + 1280 + lane * 8);
                         const size_t elem = (((size_t)meta[2 * stage + 1].x * hkv + head) * kPageTokens + (nvalid - 1)) * kHeadDim + 4 * lane;
@@ -787,17 +785,15 @@ __global__ void __launch_bounds__(kShortThreads) qm_decode_short_kernel(const De
         }
         const uint2 craw = *reinterpret_cast<const uint2*>(a.rope_cos + (size_t)position * kHeadDim + 4 * lane);
         const uint2 sraw = *reinterpret_cast<const uint2*>(a.rope_sin + (size_t)position * kHeadDim + 4 * lane);
-        const float c[4] = {bf16_lo(craw.x), bf16_hi(craw.x), bf16_lo(craw.y), bf16_hi(craw.y)};
-        const float sn[4] = {bf16_lo(sraw.x), bf16_hi(sraw.x), bf16_lo(sraw.y), bf16_hi(sraw.y)};
         const size_t new_row = tile + (size_t)(len - 1) * kHeadDim + 4 * lane;
         if (warp < 2) {
             const uint2 raw = *reinterpret_cast<const uint2*>(a.q_rot + (row0 + warp) * kHeadDim + 4 * lane);
             const uint2 wq = *reinterpret_cast<const uint2*>(a.q_norm_weight + 4 * lane);
-            *reinterpret_cast<uint2*>(qrows + warp * 256 + lane * 8) = norm_rope_row(raw, wq, c, sn, lane, a.epsilon);
+            *reinterpret_cast<uint2*>(qrows + warp * 256 + lane * 8) = norm_rope_row(raw, wq, craw, sraw, lane, a.epsilon);
         } else if (warp == 2) {
             const uint2 raw = *reinterpret_cast<const uint2*>(a.raw_k + (size_t)seg * kHeadDim + 4 * lane);
             const uint2 wk = *reinterpret_cast<const uint2*>(a.k_norm_weight + 4 * lane);
-            const uint2 krow = norm_rope_row(raw, wk, c, sn, lane, a.epsilon);
+            const uint2 krow = norm_rope_row(raw, wk, craw, sraw, lane, a.epsilon);
             *reinterpret_cast<uint2*>(ktile + (len - 1) * (kHeadDim * 2) + lane * 8) = krow;
             *reinterpret_cast<uint2*>(a.key_pool + new_row) = krow;
         } else {

@@ -173,3 +173,69 @@ def test_second_chunk_attends_the_cache_of_the_first(qm):
             assert m["max_abs"] <= TOL_MAX_ABS and m["mean_rel"] <= TOL_MEAN_REL, (part, m)
     finally:
         eng.close()
+
+
+def test_eight_rows_per_warp_equals_four_rows_per_warp(qm):
+    """With 16 + 8 heads a warp of the append kernels takes eight head rows and reduces their sums of squares
+    together; with 8 + 4 heads it takes four and reduces each on its own.  The same rows through both must give the same bits, non-finite rows and rows whose
+    squares overflow included, and such a row must not leak into its seven neighbours."""
+    big = scenario.PrefillScenario(41, [37, 5, 64], q_heads=16, kv_heads=8, random_weights=True)
+    big.q[3, 2, 17] = 0x7F80            # +inf
+    big.q[3, 5, 0] = 0x7FC1             # NaN with a payload
+    big.q[9, 11, 127] = 0xFF80          # -inf
+    big.q[20, 1, :] = 0x7F00            # 1.7e38: every square overflows
+    big.k[3, 0, 64] = 0x7F80
+    big.k[9, 3, 1] = 0xFFC0
+    big.k[30, 2, 5] = 0x7E80            # one overflowing square in an otherwise ordinary row
+    small = scenario.PrefillScenario(41, [37, 5, 64], q_heads=8, kv_heads=4, random_weights=True)
+    small.q, small.k, small.v = (np.ascontiguousarray(x) for x in (big.q[:, :8], big.k[:, :4], big.v[:, :4]))
+    small.q_w, small.k_w, small.page_table = big.q_w, big.k_w, big.page_table
+    assert small.num_pages == big.num_pages
+    got_big = scenario.run_prefill_on_gpu(qm, big, attention=False)
+    got_small = scenario.run_prefill_on_gpu(qm, small, attention=False)
+    assert got_big["status"] == 0 and got_small["status"] == 0
+    assert np.array_equal(got_big["q_rot"][:, :8], got_small["q_rot"])
+    kb = got_big["key_pool"].reshape(big.num_pages, 8, 64, 128)
+    ks = got_small["key_pool"].reshape(big.num_pages, 4, 64, 128)
+    vb = got_big["value_pool"].reshape(big.num_pages, 8, 64, 128)
+    vs = got_small["value_pool"].reshape(big.num_pages, 4, 64, 128)
+    assert np.array_equal(kb[:, :4], ks) and np.array_equal(vb[:, :4], vs)
+    # the rows next to a non-finite one are ordinary numbers, and the heads the small run does not have agree with
+    # the oracle like any other row
+    finite_rows = np.ones(big.q.shape[:2], dtype=bool)
+    for t, h in ((3, 2), (3, 5), (9, 11), (20, 1)):
+        finite_rows[t, h] = False
+    want_q, _, _ = big.expected_append()
+    assert_roped_close(got_big["q_rot"][finite_rows], want_q[finite_rows])
+    assert np.isfinite(oracle.bf16_to_f32(got_big["q_rot"][finite_rows])).all()
+
+
+def test_inputs_a_bulk_copy_cannot_read_take_the_one_shot_kernel_with_the_same_bits(qm):
+    """Packed prompts go through the ring of bulk copies when q, k and v start on 16-byte boundaries; inputs that
+    are only 8-byte aligned (the ABI's requirement) go through the one-shot kernel.  Same rows, same bits."""
+    import torch
+
+    ps = scenario.PrefillScenario(43, [150, 3, 77], random_weights=True)
+    aligned = scenario.run_prefill_on_gpu(qm, ps, attention=False)
+    eng = qm.TalkerAttention(layers=1, num_pages=ps.num_pages, q_heads=ps.q_heads, kv_heads=ps.kv_heads,
+                             max_positions=max(ps.max_pos, 1))
+    try:
+        def shifted(bits):
+            flat = torch.zeros(bits.size + 4, dtype=torch.bfloat16, device="cuda")
+            view = flat[4:].view(*bits.shape)            # starts 8 bytes after a 16-byte boundary
+            view.copy_(scenario._bf16_tensor(torch, bits))
+            assert view.data_ptr() % 16 == 8
+            return view
+        q, k, v = shifted(ps.q), shifted(ps.k), shifted(ps.v)
+        qw, kw = scenario._bf16_tensor(torch, ps.q_w), scenario._bf16_tensor(torch, ps.k_w)
+        cu = torch.from_numpy(ps.cu_seqlens).cuda()
+        page_table = torch.from_numpy(np.maximum(ps.page_table, 0)).cuda()
+        q_rot = eng.prefill_norm_rope_scatter(0, q, k, v, qw, kw, cu, page_table)
+        torch.cuda.synchronize()
+        kview, vview = eng.pool_view(0)
+        assert eng.status() == 0
+        assert np.array_equal(scenario._bits(q_rot), aligned["q_rot"])
+        assert np.array_equal(scenario._bits(kview), aligned["key_pool"])
+        assert np.array_equal(scenario._bits(vview), aligned["value_pool"])
+    finally:
+        eng.close()
