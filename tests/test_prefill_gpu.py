@@ -239,3 +239,43 @@ def test_inputs_a_bulk_copy_cannot_read_take_the_one_shot_kernel_with_the_same_b
         assert np.array_equal(scenario._bits(vview), aligned["value_pool"])
     finally:
         eng.close()
+
+
+def test_prefill_append_rejects_bad_pages_and_positions_without_writing(qm):
+    """A page id outside the pool, a prompt longer than its page table and a position past the RoPE table set their
+    status bits; the rows concerned are not written, every other row is."""
+    import torch
+
+    eng = qm.TalkerAttention(layers=1, num_pages=6, max_positions=160)
+    try:
+        lengths = [130, 70, 200]                       # stream 2 runs past the 160 RoPE rows
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)).cuda()
+        total = int(sum(lengths))
+        q = torch.randn(total, 16, 128, device="cuda").to(torch.bfloat16)
+        k = torch.randn(total, 8, 128, device="cuda").to(torch.bfloat16)
+        v = torch.randn(total, 8, 128, device="cuda").to(torch.bfloat16)
+        w = torch.ones(128, device="cuda", dtype=torch.bfloat16)
+        # stream 0: second page id outside the pool, no third page (its tokens 128, 129 have nowhere to go);
+        # stream 1: fine; stream 2: pages 3, 4 only
+        table = torch.tensor([[0, 99], [1, 2], [3, 4]], dtype=torch.int32, device="cuda")
+        q_rot = torch.full_like(q, 7.0)
+        eng.prefill_norm_rope_scatter(0, q, k, v, w, w, cu, table, q_rot=q_rot)
+        torch.cuda.synchronize()
+        bits = eng.status()
+        assert bits & qm.DEVSTAT_BAD_PAGE and bits & qm.DEVSTAT_BAD_POS and not bits & qm.DEVSTAT_TIMEOUT
+        kview, vview = eng.pool_view(0)
+        kview = kview.view(6, 8, 64, 128)
+        vview = vview.view(6, 8, 64, 128)
+        # stream 1 landed whole: V rows are copies
+        want = v[130:200].permute(1, 0, 2)
+        assert torch.equal(vview[1, :, :64], want[:, :64]) and torch.equal(vview[2, :, :6], want[:, 64:70])
+        # stream 0: first page written, nothing anywhere else for it (page 5 is nobody's and stays zero)
+        assert torch.equal(vview[0], v[0:64].permute(1, 0, 2))
+        assert not vview[5].float().abs().max().item() and not kview[5].float().abs().max().item()
+        # stream 2: positions 0 .. 127 written (pages 3, 4), positions 128 .. 159 roped but without a cache row,
+        # positions >= 160 untouched (q_rot keeps its fill)
+        assert torch.equal(vview[3], v[200:264].permute(1, 0, 2)) and torch.equal(vview[4], v[264:328].permute(1, 0, 2))
+        assert (q_rot[200 + 160:] == 7.0).all()
+        assert not (q_rot[200:200 + 160] == 7.0).all(dim=-1).any()
+    finally:
+        eng.close()
