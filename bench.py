@@ -530,25 +530,34 @@ def run_ours(args):
     eng.close()
     del q, k, v, q_rot, out
     torch.cuda.empty_cache()
-    if not args.no_prefill:
-        prefill = run_prefill_section(pkg, max(3, min(args.steps, 10)), args.warmup, check=rank == 0)
+    def guarded(name, section):
+        """A secondary section that raises must not take the primary line down with it: its entry then holds the
+        error text instead of figures (every rank takes the same path when the error is one every rank meets)."""
+        try:
+            return section()
+        except Exception as exc:
+            sys.stderr.write(f"bench.py: section {name} failed: {type(exc).__name__}: {exc}\n")
+            return {"error": f"{type(exc).__name__}: {exc}"[:400]}
+
+    def summed_over_ranks(entry, key, total_key):
         if world > 1:
-            t = torch.tensor([prefill["tflops"]], device="cuda", dtype=torch.float64)
+            t = torch.tensor([entry.get(key, 0.0) or 0.0], device="cuda", dtype=torch.float64)
             dist.all_reduce(t)
-            prefill["tflops_all_gpus"] = float(t.item())
+            entry[total_key] = float(t.item())
+
+    if not args.no_prefill:
+        prefill = guarded("prefill", lambda: run_prefill_section(pkg, max(3, min(args.steps, 10)), args.warmup, check=rank == 0))
+        summed_over_ranks(prefill, "tflops", "tflops_all_gpus")
         line["prefill"] = prefill
     if not args.no_long_context:
-        line["long_context"] = run_long_context_section(pkg, world, rank, args.steps)
+        line["long_context"] = guarded("long_context", lambda: run_long_context_section(pkg, world, rank, args.steps))
     if not args.no_single_stream and rank == 0:
-        line["single_stream"] = run_single_stream_section(pkg, args.steps)
+        line["single_stream"] = guarded("single_stream", lambda: run_single_stream_section(pkg, args.steps))
     if not args.no_talker_step and rank == 0:
-        line["code_predictor"] = run_code_predictor_section(pkg, args.steps)
+        line["code_predictor"] = guarded("code_predictor", lambda: run_code_predictor_section(pkg, args.steps))
     if not args.no_talker_step:
-        talker = run_talker_step_section(pkg, args.steps)
-        if world > 1:
-            t = torch.tensor([talker["tokens_per_s"]], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t)
-            talker["tokens_per_s_all_gpus"] = float(t.item())
+        talker = guarded("talker_step", lambda: run_talker_step_section(pkg, args.steps))
+        summed_over_ranks(talker, "tokens_per_s", "tokens_per_s_all_gpus")
         line["talker_step"] = talker
     if rank == 0:
         # the figures a reader looks for first, ahead of everything else on the line
