@@ -210,12 +210,13 @@ def test_eight_rows_per_warp_equals_four_rows_per_warp(qm):
     assert np.isfinite(oracle.bf16_to_f32(got_big["q_rot"][finite_rows])).all()
 
 
-def test_inputs_a_bulk_copy_cannot_read_take_the_one_shot_kernel_with_the_same_bits(qm):
+@pytest.mark.parametrize("lengths", [[150, 3, 77], [5192, 4730, 1554, 3417]])
+def test_inputs_a_bulk_copy_cannot_read_take_the_one_shot_kernel_with_the_same_bits(qm, lengths):
     """Packed prompts go through the ring of bulk copies when q, k and v start on 16-byte boundaries; inputs that
     are only 8-byte aligned (the ABI's requirement) go through the one-shot kernel.  Same rows, same bits."""
     import torch
 
-    ps = scenario.PrefillScenario(43, [150, 3, 77], random_weights=True)
+    ps = scenario.PrefillScenario(43, lengths, random_weights=True)      # the second case: 14 893 tokens, 4 prompts of the bench's 8
     aligned = scenario.run_prefill_on_gpu(qm, ps, attention=False)
     eng = qm.TalkerAttention(layers=1, num_pages=ps.num_pages, q_heads=ps.q_heads, kv_heads=ps.kv_heads,
                              max_positions=max(ps.max_pos, 1))
