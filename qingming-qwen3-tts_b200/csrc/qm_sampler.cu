@@ -30,7 +30,8 @@
 
 namespace {
 
-constexpr int kSampleThreads = 256;
+constexpr int kSampleThreads = 1024;          // one CTA per stream and few streams: the threads are free
+constexpr int kParallelWeights = 1024;        // top-k weights worked out one per thread up to this k
 constexpr int kSortSize = 4096;              // as the reference's kGpuSamplerSortSize
 constexpr int kBitmapWords = kSortSize / 32;
 
@@ -105,7 +106,11 @@ __global__ void __launch_bounds__(kSampleThreads) qm_final_head_sample_kernel(co
 
     const uint16_t* row = a.logits + (size_t)stream * a.vocab;
     const float reciprocal = __uint_as_float(0x3f73cf3eu);       // float(1) / float(1.05), as 17.cu:14092
-    for (int token = tid; token < kSortSize; token += kSampleThreads) {
+    // Only the first power of two that holds the vocabulary is ordered: the padding keys are worse than any real
+    // entry, so the entries beyond it would stay where they are anyway.
+    int sort_size = 32;
+    while (sort_size < a.vocab) sort_size <<= 1;
+    for (int token = tid; token < sort_size; token += kSampleThreads) {
         unsigned long long key = 0ull;                            // padding: worse than any real entry
         if (token < a.vocab) {
             float score = bf16_bits_to_f32(row[token]);
@@ -126,7 +131,7 @@ __global__ void __launch_bounds__(kSampleThreads) qm_final_head_sample_kernel(co
     if (a.top_k <= 0) {
         // greedy: the largest key
         unsigned long long best = 0ull;
-        for (int i = tid; i < kSortSize; i += kSampleThreads) best = keys[i] > best ? keys[i] : best;
+        for (int i = tid; i < sort_size; i += kSampleThreads) best = keys[i] > best ? keys[i] : best;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) {
             const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, off);
@@ -141,9 +146,9 @@ __global__ void __launch_bounds__(kSampleThreads) qm_final_head_sample_kernel(co
         }
     } else {
         // bitonic sort, descending
-        for (int width = 2; width <= kSortSize; width <<= 1) {
+        for (int width = 2; width <= sort_size; width <<= 1) {
             for (int stride = width >> 1; stride > 0; stride >>= 1) {
-                for (int index = tid; index < kSortSize; index += kSampleThreads) {
+                for (int index = tid; index < sort_size; index += kSampleThreads) {
                     const int partner = index ^ stride;
                     if (partner <= index) continue;
                     const bool descending = (index & width) == 0;
@@ -156,19 +161,27 @@ __global__ void __launch_bounds__(kSampleThreads) qm_final_head_sample_kernel(co
                 __syncthreads();
             }
         }
+        // The k weights exp((score - best) / temperature), in double as the reference has them.  One thread each
+        // works them out (the exponentials are the expensive part); thread 0 then adds them up and walks the
+        // cumulative sum in the reference's order, so the sums are the same bits as its serial loop's.
+        __shared__ double weight[kParallelWeights];
+        const int keep = a.top_k < a.vocab ? a.top_k : a.vocab;
+        const double inv_t = 1.0 / (double)a.temperature;
+        const double maximum = (double)key_score(keys[0]) * inv_t;
+        const bool parallel = keep <= kParallelWeights;
+        if (parallel && tid < keep) weight[tid] = exp((double)key_score(keys[tid]) * inv_t - maximum);
+        __syncthreads();
         if (tid == 0) {
-            const int keep = a.top_k < a.vocab ? a.top_k : a.vocab;
-            const double inv_t = 1.0 / (double)a.temperature;
-            const double maximum = (double)key_score(keys[0]) * inv_t;
+            auto weight_of = [&](int i) { return parallel ? weight[i] : exp((double)key_score(keys[i]) * inv_t - maximum); };
             double total = 0.0;
-            for (int i = 0; i < keep; ++i) total += exp((double)key_score(keys[i]) * inv_t - maximum);
+            for (int i = 0; i < keep; ++i) total += weight_of(i);
             code = key_index(keys[0]);
             if (total > 0.0) {
                 const double target = splitmix_uniform(a.rng_state + stream) * total;
                 double cumulative = 0.0;
                 code = key_index(keys[keep - 1]);
                 for (int i = 0; i < keep; ++i) {
-                    cumulative += exp((double)key_score(keys[i]) * inv_t - maximum);
+                    cumulative += weight_of(i);
                     if (target < cumulative) {
                         code = key_index(keys[i]);
                         break;
