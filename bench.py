@@ -1013,8 +1013,8 @@ def run_single_stream_section(pkg, steps):
 def run_code_predictor_section(pkg, steps):
     """Secondary measurement: one frame of the reference's code predictor (15 steps of a 5-layer decoder, hidden
     1024, same 16 / 8 x 128 attention shape, at most 16 cached positions; 17.cu:13616-13905) for 32 streams, on the
-    same kernels as the talker step, random-init weights in the checkpoint's shapes, greedy, one CUDA graph per
-    frame as in the reference."""
+    same kernels as the talker step, random-init weights in the checkpoint's shapes, one CUDA graph per frame as in
+    the reference; timed greedy and with the reference's default sampling (top-k 50, temperature 0.9)."""
     import importlib
 
     import torch
@@ -1027,26 +1027,33 @@ def run_code_predictor_section(pkg, steps):
     runner = predictor.CodePredictor(pkg, streams, weights)
     talker_hidden = torch.randn(streams, predictor.OUTER_HIDDEN, generator=gen, device="cuda").to(torch.bfloat16)
     first_embedding = torch.randn(streams, predictor.OUTER_HIDDEN, generator=gen, device="cuda").to(torch.bfloat16)
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        for _ in range(2):
-            runner.frame(talker_hidden, first_embedding)
-    torch.cuda.current_stream().wait_stream(side)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        runner.frame(talker_hidden, first_embedding)
-    for _ in range(3):
-        graph.replay()
-    torch.cuda.synchronize()
-    n = max(5, min(steps, 20))
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(n):
-        graph.replay()
-    b.record()
-    torch.cuda.synchronize()
-    ms = a.elapsed_time(b) / n
+    rng_state = torch.arange(1, streams + 1, dtype=torch.int64, device="cuda")
+
+    def frame_ms(**sampling):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                runner.frame(talker_hidden, first_embedding, **sampling)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            runner.frame(talker_hidden, first_embedding, **sampling)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        n = max(5, min(steps, 20))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    ms = frame_ms()
+    # the reference's default for the predictor: subtalker_dosample, top_k 50, temperature 0.9 (17.cu:7139)
+    ms_sampling = frame_ms(rng_state=rng_state, top_k=50, temperature=0.9)
     status = runner.engine.status()
     runner.close()
     d = predictor.PredictorDims()
@@ -1057,7 +1064,8 @@ def run_code_predictor_section(pkg, steps):
     launches = token_steps * (d.layers * 7 + 2) + d.steps * 4
     peak, _ = load_peaks()
     return {"workload": "code_predictor_frame_1p7b_shape", "streams_per_gpu": streams, "steps_per_frame": d.steps,
-            "ms_per_frame": ms, "frames_per_s": streams / (ms * 1e-3), "kernel_launches_per_frame": launches,
+            "ms_per_frame": ms, "frames_per_s": streams / (ms * 1e-3), "ms_per_frame_top_k_50_sampling": ms_sampling,
+            "kernel_launches_per_frame": launches,
             "us_per_launch": ms * 1e3 / launches, "weight_bytes_per_frame": weight_bytes,
             "hbm_bound_ms": weight_bytes / (peak * 1e9) * 1e3, "device_status": status,
             "note": "every operator is this library's; 16 token rows per stream and frame through 5 layers; the "

@@ -80,7 +80,36 @@ __device__ __forceinline__ double splitmix_uniform(uint64_t* state) {
     return (double)(z >> 11) * (1.0 / 9007199254740992.0);
 }
 
-__global__ void __launch_bounds__(kSampleThreads) qm_final_head_sample_kernel(const SampleArgs a) {
+// 64 keys held by one warp, two per lane (elements 2 * lane and 2 * lane + 1), through the steps of a bitonic
+// network from `first_width` up to 64: first_width = 2 sorts any 64 keys, first_width = 64 merges a bitonic sequence.
+// Element pairs at a distance of 1 are the lane's own two keys, larger distances are a shuffle away.
+__device__ __forceinline__ void warp_bitonic64(unsigned long long& k0, unsigned long long& k1, int lane, int first_width,
+                                               bool descending) {
+    for (int width = first_width; width <= 64; width <<= 1) {
+        for (int stride = width >> 1; stride > 0; stride >>= 1) {
+            // direction of the pair this element is in: the sequence of `width` elements it belongs to is sorted
+            // the requested way when its index has the `width` bit clear (or width is 64), the other way otherwise
+            const bool down = (((2 * lane) & width) == 0 || width == 64) ? descending : !descending;
+            if (stride == 1) {
+                const bool swap = down ? k0 < k1 : k0 > k1;
+                if (swap) {
+                    const unsigned long long t = k0;
+                    k0 = k1;
+                    k1 = t;
+                }
+            } else {
+                const unsigned long long o0 = __shfl_xor_sync(0xffffffffu, k0, stride >> 1);
+                const unsigned long long o1 = __shfl_xor_sync(0xffffffffu, k1, stride >> 1);
+                const bool lower = ((2 * lane) & stride) == 0;            // this lane holds the pair's smaller index
+                const bool take_max = lower == down;
+                k0 = take_max ? (o0 > k0 ? o0 : k0) : (o0 < k0 ? o0 : k0);
+                k1 = take_max ? (o1 > k1 ? o1 : k1) : (o1 < k1 ? o1 : k1);
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kSampleThreads, 1) qm_final_head_sample_kernel(const SampleArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(smem);                 // [kSortSize]
     uint32_t* seen = reinterpret_cast<uint32_t*>(smem + kSortSize * sizeof(unsigned long long));   // [kBitmapWords]
@@ -108,7 +137,7 @@ __global__ void __launch_bounds__(kSampleThreads) qm_final_head_sample_kernel(co
     const float reciprocal = __uint_as_float(0x3f73cf3eu);       // float(1) / float(1.05), as 17.cu:14092
     // Only the first power of two that holds the vocabulary is ordered: the padding keys are worse than any real
     // entry, so the entries beyond it would stay where they are anyway.
-    int sort_size = 32;
+    int sort_size = 64;
     while (sort_size < a.vocab) sort_size <<= 1;
     for (int token = tid; token < sort_size; token += kSampleThreads) {
         unsigned long long key = 0ull;                            // padding: worse than any real entry
@@ -144,8 +173,44 @@ __global__ void __launch_bounds__(kSampleThreads) qm_final_head_sample_kernel(co
             for (int w = 1; w < kSampleThreads / 32; ++w) best = keys[w] > best ? keys[w] : best;
             code = best ? key_index(best) : 0;
         }
+    } else if (a.top_k <= 64) {
+        // The 64 best keys, in order, are all a draw among at most 64 needs.  Every warp sorts blocks of 64 keys in
+        // its registers (even blocks descending, odd ones ascending); then, level by level, the element-wise maximum
+        // of a descending and an ascending block is the best 64 of the two as a bitonic sequence, which one more
+        // merge puts in order.  The keys are distinct (the index is part of them), so what ends up in keys[0..63]
+        // is exactly what a full sort would have put there.
+        const int warp = tid >> 5, lane = tid & 31;
+        constexpr int kWarps = kSampleThreads / 32;
+        int blocks = sort_size >> 6;
+        for (int b = warp; b < blocks; b += kWarps) {
+            unsigned long long k0 = keys[b * 64 + 2 * lane], k1 = keys[b * 64 + 2 * lane + 1];
+            warp_bitonic64(k0, k1, lane, 2, (b & 1) == 0 || blocks == 1);
+            keys[b * 64 + 2 * lane] = k0;
+            keys[b * 64 + 2 * lane + 1] = k1;
+        }
+        __syncthreads();
+        while (blocks > 1) {
+            const int pairs = blocks >> 1;
+            unsigned long long m0[2], m1[2];                // a warp takes at most two pairs (4096 keys, 32 warps)
+            int mine = 0;
+            for (int p = warp; p < pairs; p += kWarps, ++mine) {
+                const unsigned long long* x = keys + (2 * p) * 64 + 2 * lane;
+                const unsigned long long* y = x + 64;
+                m0[mine] = x[0] > y[0] ? x[0] : y[0];
+                m1[mine] = x[1] > y[1] ? x[1] : y[1];
+            }
+            __syncthreads();                                 // everyone has read before anyone writes
+            mine = 0;
+            for (int p = warp; p < pairs; p += kWarps, ++mine) {
+                warp_bitonic64(m0[mine], m1[mine], lane, 64, (p & 1) == 0 || pairs == 1);
+                keys[p * 64 + 2 * lane] = m0[mine];
+                keys[p * 64 + 2 * lane + 1] = m1[mine];
+            }
+            __syncthreads();
+            blocks = pairs;
+        }
     } else {
-        // bitonic sort, descending
+        // bitonic sort of everything, descending
         for (int width = 2; width <= sort_size; width <<= 1) {
             for (int stride = width >> 1; stride > 0; stride >>= 1) {
                 for (int index = tid; index < sort_size; index += kSampleThreads) {
@@ -161,6 +226,8 @@ __global__ void __launch_bounds__(kSampleThreads) qm_final_head_sample_kernel(co
                 __syncthreads();
             }
         }
+    }
+    if (a.top_k > 0) {
         // The k weights exp((score - best) / temperature), in double as the reference has them.  One thread each
         // works them out (the exponentials are the expensive part); thread 0 then adds them up and walks the
         // cumulative sum in the reference's order, so the sums are the same bits as its serial loop's.

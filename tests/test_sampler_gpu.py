@@ -74,6 +74,35 @@ def test_batch_of_streams_each_with_its_own_history_and_state(engine):
             assert history[i][c.generation_index] == want[0]
 
 
+@pytest.mark.parametrize("vocab,top_k", [(2048, 50), (3072, 64), (3072, 65), (3072, 200), (4096, 50), (50, 50), (70, 8),
+                                         (64, 64), (65, 3), (1, 5), (2048, 5000)])
+def test_top_k_selection_paths_against_the_oracle(engine, vocab, top_k):
+    """Up to 64 candidates the kernel selects the best 64 keys with per-warp bitonic networks, beyond that it sorts
+    everything; small vocabularies leave most of the first block as padding.  Eight draws per shape, some with
+    ties between equal scores, each against the oracle: code and SplitMix64 state."""
+    import torch
+
+    rng = np.random.default_rng(1000 * vocab + top_k)
+    streams = 8
+    values = (rng.standard_normal((streams, vocab)) * 3.0).astype(np.float32)
+    values[1] = np.round(values[1] * 4) / 4               # many exactly equal scores
+    values[2] = 0.0                                       # all equal
+    bits = oracle.f32_to_bf16(values)
+    states = rng.integers(1, 2**62, size=streams)
+    logits = torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16)
+    state = torch.tensor(states, dtype=torch.int64, device="cuda")
+    codes = engine.final_head_sample(logits, flags=0, eos_token=0, reserved_begin=vocab, top_k=top_k, temperature=0.9,
+                                     rng_state=state)
+    torch.cuda.synchronize()
+    assert engine.status() == 0
+    codes, state = codes.cpu().numpy(), state.cpu().numpy().astype(np.uint64)
+    for i in range(streams):
+        want = oracle.final_head_sample(bits[i], np.zeros(8, dtype=np.int32), 0, 0, eos_token=0, top_k=top_k, temperature=0.9,
+                                        rng_state=int(states[i]), reserved_begin=vocab)
+        assert codes[i] == want[0], (i, codes[i], want[0])
+        assert int(state[i]) == want[2]
+
+
 def test_consecutive_steps_draw_from_the_state_in_order(engine):
     import torch
 
