@@ -229,17 +229,35 @@ __global__ void __launch_bounds__(kSampleThreads, 1) qm_final_head_sample_kernel
     }
     if (a.top_k > 0) {
         // The k weights exp((score - best) / temperature), in double as the reference has them.  One thread each
-        // works them out (the exponentials are the expensive part); thread 0 then adds them up and walks the
-        // cumulative sum in the reference's order, so the sums are the same bits as its serial loop's.
+        // works them out (the exponentials are the expensive part).  Thread 0 adds them up in the reference's order;
+        // its running sums are the reference's cumulative sums as well as, at the end, its total (both loops of the
+        // reference add the same numbers in the same order), so they are kept, and the first one above the draw is
+        // then found by all threads at once.
         __shared__ double weight[kParallelWeights];
+        __shared__ double drawn;
+        __shared__ int first_above;
         const int keep = a.top_k < a.vocab ? a.top_k : a.vocab;
         const double inv_t = 1.0 / (double)a.temperature;
         const double maximum = (double)key_score(keys[0]) * inv_t;
-        const bool parallel = keep <= kParallelWeights;
-        if (parallel && tid < keep) weight[tid] = exp((double)key_score(keys[tid]) * inv_t - maximum);
-        __syncthreads();
-        if (tid == 0) {
-            auto weight_of = [&](int i) { return parallel ? weight[i] : exp((double)key_score(keys[i]) * inv_t - maximum); };
+        if (keep <= kParallelWeights) {
+            if (tid < keep) weight[tid] = exp((double)key_score(keys[tid]) * inv_t - maximum);
+            __syncthreads();
+            if (tid == 0) {
+                double running = 0.0;
+                for (int i = 0; i < keep; ++i) {
+                    running += weight[i];
+                    weight[i] = running;
+                }
+                // no draw (and no step of the generator) when the weights do not add up to something positive
+                first_above = running > 0.0 ? keep : -1;
+                drawn = running > 0.0 ? splitmix_uniform(a.rng_state + stream) * running : 0.0;
+            }
+            __syncthreads();
+            if (first_above >= 0 && tid < keep && drawn < weight[tid]) atomicMin(&first_above, tid);
+            __syncthreads();
+            if (tid == 0) code = key_index(keys[first_above < 0 ? 0 : (first_above < keep ? first_above : keep - 1)]);
+        } else if (tid == 0) {
+            auto weight_of = [&](int i) { return exp((double)key_score(keys[i]) * inv_t - maximum); };
             double total = 0.0;
             for (int i = 0; i < keep; ++i) total += weight_of(i);
             code = key_index(keys[0]);
