@@ -352,7 +352,7 @@ int sm_count_of_current_device() {
     return cached_count;
 }
 
-// Cluster size (K split): enough CTAs to occupy every SM about twice, at most 8, at most one chunk each.
+// Cluster size (K split): enough CTAs to occupy every SM about twice, at most 8, at least two chunks each.
 int choose_split(int tiles, int chunks) {
     if (const char* forced = std::getenv("QM_GEMM_SPLIT")) {       // tuning aid
         const int v = std::atoi(forced);
@@ -364,6 +364,9 @@ int choose_split(int tiles, int chunks) {
     if (split > 8) split = 8;
     if (split == 3 || split == 5 || split == 6 || split == 7) split = split >= 4 ? 4 : 2;   // power-of-two clusters only
     while (split > 1 && chunks / split < 2) split >>= 1;
+    // More CTAs than SMs with fewer than four chunks each is all fold and no streaming (the code predictor's fused
+    // QKV: K = 1024, 32 tiles): halve the cluster there.
+    while (split > 1 && chunks / split < 4 && tiles * split > target / 2) split >>= 1;
     return split;
 }
 
