@@ -80,9 +80,14 @@ __global__ void __launch_bounds__(kNormThreads) qm_rmsnorm_rows_vec_kernel(const
     extern __shared__ uint4 row_vectors[];
     __shared__ float warp_values[8];
     pdl_trigger();
+    const int vectors = dim >> 3;
+    // The norm weight is a constant of the model: this thread's first piece of it is fetched ahead of the dependency
+    // wait, so that its round trip is not left standing at the end of the kernel (rows of up to 2048 columns have no
+    // other piece).
+    uint4 first_weight = make_uint4(0u, 0u, 0u, 0u);
+    if ((int)threadIdx.x < vectors) first_weight = __ldg(reinterpret_cast<const uint4*>(weight + 8 * threadIdx.x));
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * dim;
-    const int vectors = dim >> 3;
     for (int v = threadIdx.x; v < vectors; v += kNormThreads) {
         uint4 raw = *reinterpret_cast<const uint4*>(x + base + 8 * v);
         if (hidden) {
@@ -107,7 +112,7 @@ __global__ void __launch_bounds__(kNormThreads) qm_rmsnorm_rows_vec_kernel(const
     const float inverse_rms = rsqrtf(__fadd_rn(__fdiv_rn(sum, (float)dim), epsilon));
     for (int v = threadIdx.x; v < vectors; v += kNormThreads) {
         const uint4 raw = row_vectors[v];
-        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(weight + 8 * v));
+        const uint4 wv = v == (int)threadIdx.x ? first_weight : __ldg(reinterpret_cast<const uint4*>(weight + 8 * v));
         const uint32_t* rw = reinterpret_cast<const uint32_t*>(&raw);
         const uint32_t* ww = reinterpret_cast<const uint32_t*>(&wv);
         uint4 outv;
