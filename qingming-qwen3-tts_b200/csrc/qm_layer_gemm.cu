@@ -354,10 +354,12 @@ int sm_count_of_current_device() {
 
 // Cluster size (K split): enough CTAs to occupy every SM about twice, at most 8, at least two chunks each.
 int choose_split(int tiles, int chunks) {
-    if (const char* forced = std::getenv("QM_GEMM_SPLIT")) {       // tuning aid
+#ifdef QM_DECODE_TUNING
+    if (const char* forced = std::getenv("QM_GEMM_SPLIT")) {       // tuning builds only
         const int v = std::atoi(forced);
         if (v >= 1 && v <= 8 && chunks / v >= 1) return v;
     }
+#endif
     const int target = 2 * sm_count_of_current_device();
     int split = target / (tiles > 0 ? tiles : 1);
     if (split < 1) split = 1;
